@@ -1,0 +1,75 @@
+// Shared definitions of the B200 BPE library: status helpers, the device control block and
+// the layout of the pair table.  Everything here is internal; the public surface is include/b200bpe.h.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/b200bpe.h"
+
+namespace b200bpe {
+
+constexpr uint32_t WORD_START_BIT = 0x10000u;  // reference symbol layout: bit 16 = word start
+constexpr uint32_t TOKEN_MASK = 0xFFFFu;       // low 16 bits = token id
+constexpr uint32_t INVALID_TOKEN = 0xFFFFFFFFu;
+
+// Device-side status words (DevState::status); mapped to b200bpe_status by the host.
+enum DevStatus : uint32_t { DS_OK = 0, DS_TABLE_FULL = 1, DS_LOOKBACK_TIMEOUT = 2, DS_INTERNAL = 3 };
+
+// One slot of the open-addressing pair table: 64-bit (left << 32 | right) key, 0 = empty
+// (the left symbol of a counted pair is never 0), and its count.  16 bytes so that an insert
+// touches one 32-byte sector and the arg-max pass reads whole uint4 words.
+struct __align__(16) PairSlot {
+    unsigned long long key;
+    uint32_t count;
+    uint32_t pad;
+};
+
+// Control block living in device memory; the kernels of a batch read and write it without any
+// host round trip.  The fields up to merges_done mirror the reference's IterState.
+struct DevState {
+    uint32_t n[2];          // live symbol count, indexed by (epoch & 1)
+    uint32_t epoch;         // merges applied to the symbol buffers so far (selects ping/pong)
+    uint32_t early_stop;    // IterState.early_stop: best count < 2 or ids exhausted
+    uint32_t target_hit;    // merges_done reached merges_target
+    uint32_t next_id;       // IterState.next_token_id
+    uint32_t a, b, new_id;  // winning pair and its new symbol
+    uint32_t max_count;     // count of the winning pair
+    uint32_t merges_done;   // merges logged since creation/reset
+    uint32_t merges_target; // stop once merges_done reaches this
+    uint32_t status;        // DevStatus
+    uint32_t active;        // 1 while the merge chosen by setup still has to be applied
+    uint32_t k3_epoch;      // epoch the merge/compaction kernel works on (written by setup only)
+    uint32_t ticket;        // next tile of the merge/compaction kernel
+    uint32_t argmax_done;   // CTAs of the arg-max kernel that have finished
+    uint32_t occupied;      // non-empty table slots seen by the last arg-max pass
+    uint32_t table_log2;    // log2(table capacity)
+    uint32_t literal;       // 1 = compaction input bounded by the post-merge count
+    uint32_t want_grow;     // arg-max saw the table more than half full
+    uint32_t world;         // ranks sharing the job (1 = single GPU)
+    unsigned long long best_packed;  // sharded runs: (count << 32) | ~pair32 after the all-reduce
+    uint32_t pad[8];
+};
+
+struct CtaBest {
+    unsigned long long key;
+    uint32_t count;
+    uint32_t pad;
+};
+
+void set_last_error(const std::string& s);
+
+#define B2_CUDA(expr)                                                                                   \
+    do {                                                                                                \
+        cudaError_t _e = (expr);                                                                        \
+        if (_e != cudaSuccess) {                                                                        \
+            ::b200bpe::set_last_error(std::string(#expr) + ": " + cudaGetErrorString(_e));              \
+            return (_e == cudaErrorMemoryAllocation) ? B200BPE_ERR_OOM : B200BPE_ERR_CUDA;              \
+        }                                                                                               \
+    } while (0)
+
+struct Ctx;  // defined in api.cu
+
+}  // namespace b200bpe

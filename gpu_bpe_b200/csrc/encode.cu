@@ -1,0 +1,622 @@
+// Trie encoding on the device: chunk-bounded greedy longest match, then a single-pass
+// scan + compaction of the per-chunk token runs.  Replaces trie_tokenizer_chunked,
+// trie_prefix_sum and trie_tokenizer_compact (src/bpe/tokenizer/tokenize.wgsl:88-243 of the
+// reference) and the host flow of TrieTokenizer.#encodeSinglePass (tokenizer.js:213-335).
+//
+// Device layout of the trie (built once per tokenizer from the v3 binary):
+//   * root_lut[256]   byte → packed child of the root, staged in shared memory by every CTA
+//   * trans           open-addressing table (parent << 8 | byte) → packed child, 8 bytes per slot,
+//                     at most half full, pinned in L2 with an access-policy window
+//   * node_tok[]      node → token id, read once per emitted token
+// A packed child is  index | has_token << 31 | is_leaf << 30, so a step of the walk is one
+// table probe and needs no second load to learn whether the new node ends a token or has
+// children.  Each CTA also keeps a direct-mapped shared-memory cache of recent probes.
+#include <algorithm>
+#include <cstring>
+#include <vector>
+
+#include "ctx.cuh"
+
+namespace b200bpe {
+
+constexpr uint32_t T_MISS = 0xFFFFFFFFu;
+constexpr uint32_t T_EMPTY_KEY = 0xFFFFFFFFu;
+constexpr uint32_t T_HAS_TOKEN = 0x80000000u, T_LEAF = 0x40000000u, T_INDEX = 0x3FFFFFFFu;
+
+constexpr int TW_THREADS = 512;
+constexpr int TW_CACHE_LOG2 = 13;  // 8192 entries * 8 B = 64 KB per CTA
+constexpr int SC_THREADS = 256;    // scan/compaction: chunks per tile
+constexpr uint32_t SC_MAX_SPINS = 1u << 22;
+
+struct TrieDev {
+    const uint32_t* root_lut;
+    const uint2* trans;
+    uint32_t trans_mask;
+    const uint32_t* node_tok;
+};
+
+__device__ __forceinline__ uint32_t hash_edge(uint32_t key) {
+    uint32_t x = key;
+    x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+    return x;
+}
+static inline uint32_t hash_edge_host(uint32_t key) {
+    uint32_t x = key;
+    x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+    return x;
+}
+
+// Where chunk g starts and ends.  Single buffer: fixed stride.  Batch: chunks are numbered
+// document by document (chunk_base = exclusive scan of per-document chunk counts) and never
+// span two documents, exactly as separate encodeBytes calls would cut them.
+__device__ __forceinline__ void chunk_span(uint64_t g, uint32_t cs, uint64_t n, const uint64_t* __restrict__ doc_off,
+                                           const uint64_t* __restrict__ chunk_base, uint32_t n_docs, uint64_t* lo,
+                                           uint64_t* hi) {
+    if (!doc_off) {
+        *lo = g * cs;
+        *hi = min(n, *lo + cs);
+        return;
+    }
+    uint32_t a = 0, b = n_docs;  // last d with chunk_base[d] <= g
+    while (b - a > 1) {
+        const uint32_t m = (a + b) >> 1;
+        if (chunk_base[m] <= g) a = m; else b = m;
+    }
+    *lo = doc_off[a] + (g - chunk_base[a]) * cs;
+    *hi = min(doc_off[a + 1], *lo + cs);
+}
+
+struct ByteWindow {
+    const uint4* base4;
+    uint64_t shift;   // misalignment of the byte pointer
+    uint64_t idx;
+    uint4 v;
+    __device__ __forceinline__ uint32_t get(uint64_t pos) {
+        const uint64_t ap = pos + shift;
+        const uint64_t i = ap >> 4;
+        if (i != idx) { v = __ldg(base4 + i); idx = i; }
+        const uint32_t w = (uint32_t)(ap >> 2) & 3u;
+        const uint32_t word = w == 0 ? v.x : w == 1 ? v.y : w == 2 ? v.z : v.w;
+        return (word >> (((uint32_t)ap & 3u) * 8u)) & 0xFFu;
+    }
+};
+
+template <int THREADS, int CACHE_LOG2>
+__global__ void __launch_bounds__(THREADS)
+k_trie_walk(TrieDev t, const uint8_t* __restrict__ bytes, uint64_t n, uint32_t cs, const uint64_t* __restrict__ doc_off,
+            const uint64_t* __restrict__ chunk_base, uint32_t n_docs, uint64_t n_chunks_static,
+            uint32_t* __restrict__ staging, uint32_t* __restrict__ counts) {
+    extern __shared__ __align__(16) unsigned char tw_smem[];
+    uint2* cache = reinterpret_cast<uint2*>(tw_smem);
+    uint32_t* lut = reinterpret_cast<uint32_t*>(cache + (1 << CACHE_LOG2));
+    for (int i = threadIdx.x; i < (1 << CACHE_LOG2); i += THREADS) cache[i] = make_uint2(T_EMPTY_KEY, 0u);
+    for (int i = threadIdx.x; i < 256; i += THREADS) lut[i] = t.root_lut[i];
+    __syncthreads();
+    const uint64_t n_chunks = doc_off ? chunk_base[n_docs] : n_chunks_static;
+    ByteWindow win;
+    win.shift = reinterpret_cast<uintptr_t>(bytes) & 15u;
+    win.base4 = reinterpret_cast<const uint4*>(reinterpret_cast<uintptr_t>(bytes) - win.shift);
+    win.idx = ~0ull;
+
+    for (uint64_t g = (uint64_t)blockIdx.x * THREADS + threadIdx.x; g < n_chunks; g += (uint64_t)gridDim.x * THREADS) {
+        uint64_t pos, ce;
+        chunk_span(g, cs, n, doc_off, chunk_base, n_docs, &pos, &ce);
+        uint32_t* __restrict__ out = staging + g * cs;
+        uint32_t tw = 0;
+        while (pos < ce) {
+            const uint32_t first = win.get(pos);
+            uint32_t v = lut[first];
+            if (v == T_MISS) { out[tw++] = first; pos++; continue; }
+            uint64_t wp = pos + 1, lmp = pos;
+            uint32_t last = T_MISS;
+            if (v & T_HAS_TOKEN) { last = v & T_INDEX; lmp = wp; }
+            while (!(v & T_LEAF) && wp < ce) {
+                const uint32_t key = ((v & T_INDEX) << 8) | win.get(wp);
+                const uint32_t h = hash_edge(key);
+                const uint2 ce2 = cache[h & ((1 << CACHE_LOG2) - 1)];
+                uint32_t nv;
+                if (ce2.x == key) {
+                    nv = ce2.y;
+                } else {
+                    uint32_t slot = (h >> 7) & t.trans_mask;
+                    for (;;) {
+                        const uint2 e = __ldg(t.trans + slot);
+                        if (e.x == key) { nv = e.y; break; }
+                        if (e.x == T_EMPTY_KEY) { nv = T_MISS; break; }
+                        slot = (slot + 1) & t.trans_mask;
+                    }
+                    cache[h & ((1 << CACHE_LOG2) - 1)] = make_uint2(key, nv);
+                }
+                if (nv == T_MISS) break;
+                v = nv;
+                wp++;
+                if (v & T_HAS_TOKEN) { last = v & T_INDEX; lmp = wp; }
+            }
+            if (last != T_MISS) { out[tw++] = __ldg(t.node_tok + last); pos = lmp; }
+            else { out[tw++] = first; pos++; }
+        }
+        counts[g] = tw;
+    }
+}
+
+// Per-document chunk counts → exclusive scan (one CTA; documents are few compared with bytes).
+__global__ void __launch_bounds__(1024)
+k_doc_chunk_scan(const uint64_t* __restrict__ doc_off, uint32_t n_docs, uint32_t cs, uint64_t* __restrict__ chunk_base) {
+    __shared__ uint64_t wsum[32];
+    __shared__ uint64_t carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint32_t b = 0; b < n_docs; b += 1024) {
+        const uint32_t d = b + threadIdx.x;
+        uint64_t c = 0;
+        if (d < n_docs) c = (doc_off[d + 1] - doc_off[d] + cs - 1) / cs;
+        uint64_t incl = c;
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint64_t x = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if (lane >= o) incl += x;
+        }
+        if (lane == 31) wsum[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            uint64_t w = wsum[lane], wi = w;
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint64_t x = __shfl_up_sync(0xFFFFFFFFu, wi, o);
+                if (lane >= o) wi += x;
+            }
+            wsum[lane] = wi - w;
+        }
+        __syncthreads();
+        const uint64_t excl = carry + wsum[warp] + incl - c;
+        if (d < n_docs) chunk_base[d] = excl;
+        __syncthreads();
+        if (threadIdx.x == 1023) carry = excl + c;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) chunk_base[n_docs] = carry;
+}
+
+// Tile descriptor of the look-back: bits 63..62 = flag (1 aggregate, 2 prefix), low 62 bits = value.
+__device__ __forceinline__ unsigned long long ld_d64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_d64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+// One tile = SC_THREADS chunks.  Sum the tile's token counts, learn the tile's offset by
+// decoupled look-back, then copy every chunk's run from its stride-`cs` staging slot to its final
+// place with coalesced warp copies.  ctl[0] = tile ticket, ctl[1] = error flag; total → *total_out.
+__global__ void __launch_bounds__(SC_THREADS)
+k_scan_compact(const uint32_t* __restrict__ staging, const uint32_t* __restrict__ counts, uint32_t cs,
+               const uint64_t* __restrict__ chunk_base, uint32_t n_docs, uint64_t n_chunks_static,
+               unsigned long long* __restrict__ desc, uint32_t* __restrict__ ctl, uint64_t* __restrict__ chunk_offsets,
+               uint32_t* __restrict__ out, uint64_t cap, uint64_t* __restrict__ total_out) {
+    __shared__ uint64_t s_off[SC_THREADS];
+    __shared__ uint32_t s_cnt[SC_THREADS];
+    __shared__ uint32_t wsum[SC_THREADS / 32];
+    __shared__ uint32_t s_tile;
+    __shared__ uint64_t s_base;
+    const uint64_t n_chunks = chunk_base ? chunk_base[n_docs] : n_chunks_static;
+    const uint64_t ntiles = (n_chunks + SC_THREADS - 1) / SC_THREADS;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (n_chunks == 0) {
+        if (blockIdx.x == 0 && threadIdx.x == 0) {
+            *total_out = 0;
+            if (chunk_offsets) chunk_offsets[0] = 0;
+        }
+        return;
+    }
+    for (;;) {
+        __syncthreads();
+        if (threadIdx.x == 0) s_tile = atomicAdd(&ctl[0], 1u);
+        __syncthreads();
+        const uint64_t tile = s_tile;
+        if (tile >= ntiles) break;
+        const uint64_t g = tile * SC_THREADS + threadIdx.x;
+        const uint32_t c = g < n_chunks ? counts[g] : 0u;
+        uint32_t incl = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t x = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if (lane >= o) incl += x;
+        }
+        if (lane == 31) wsum[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            const uint32_t w = lane < SC_THREADS / 32 ? wsum[lane] : 0u;
+            uint32_t wi = w;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t x = __shfl_up_sync(0xFFFFFFFFu, wi, o);
+                if (lane >= o) wi += x;
+            }
+            if (lane < SC_THREADS / 32) wsum[lane] = wi - w;
+            const unsigned long long agg = __shfl_sync(0xFFFFFFFFu, wi, SC_THREADS / 32 - 1);
+            unsigned long long excl = 0ull;
+            if (tile == 0) {
+                if (lane == 0) st_d64(desc, (2ull << 62) | agg);
+            } else {
+                if (lane == 0) st_d64(desc + tile, (1ull << 62) | agg);
+                long long pos = (long long)tile - 1;
+                uint32_t spins = 0;
+                bool timed_out = false;
+                for (;;) {
+                    const long long idx = pos - lane;
+                    unsigned long long d = 2ull << 62;  // before tile 0: a zero prefix
+                    for (;;) {
+                        if (idx >= 0) d = ld_d64(desc + idx);
+                        if (__all_sync(0xFFFFFFFFu, (d >> 62) != 0ull)) break;
+                        if (++spins > SC_MAX_SPINS) { timed_out = true; break; }
+                        __nanosleep(40);
+                    }
+                    if (timed_out) break;
+                    const uint32_t pmask = __ballot_sync(0xFFFFFFFFu, (d >> 62) == 2ull);
+                    const int first = pmask ? (__ffs(pmask) - 1) : 32;
+                    unsigned long long contrib = (lane <= first) ? (d & 0x3FFFFFFFFFFFFFFFull) : 0ull;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xFFFFFFFFu, contrib, o);
+                    excl += contrib;
+                    if (pmask) break;
+                    pos -= 32;
+                }
+                if (timed_out) {
+                    if (lane == 0) atomicExch(&ctl[1], 1u);
+                    excl = 0ull;
+                }
+                if (lane == 0) st_d64(desc + tile, (2ull << 62) | (excl + agg));
+            }
+            if (lane == 0) {
+                s_base = excl;
+                if (tile == ntiles - 1) {
+                    *total_out = excl + agg;
+                    if (chunk_offsets) chunk_offsets[n_chunks] = excl + agg;
+                }
+            }
+        }
+        __syncthreads();
+        const uint64_t off = s_base + wsum[warp] + (incl - c);
+        s_off[threadIdx.x] = off;
+        s_cnt[threadIdx.x] = c;
+        if (chunk_offsets && g < n_chunks) chunk_offsets[g] = off;
+        __syncthreads();
+        for (int k = warp; k < SC_THREADS; k += SC_THREADS / 32) {
+            const uint32_t cnt = s_cnt[k];
+            if (cnt == 0u) continue;
+            const uint64_t o = s_off[k];
+            const uint32_t* __restrict__ src = staging + (tile * SC_THREADS + k) * (uint64_t)cs;
+            for (uint32_t i = lane; i < cnt; i += 32)
+                if (o + i < cap) out[o + i] = src[i];
+        }
+    }
+}
+
+__global__ void k_doc_token_offsets(const uint64_t* __restrict__ chunk_base, const uint64_t* __restrict__ chunk_offsets,
+                                    uint32_t n_docs, uint64_t* __restrict__ tok_offsets) {
+    for (uint32_t d = blockIdx.x * blockDim.x + threadIdx.x; d <= n_docs; d += gridDim.x * blockDim.x)
+        tok_offsets[d] = chunk_offsets[chunk_base[d]];
+}
+
+struct Tokenizer {
+    Ctx* ctx = nullptr;
+    uint32_t node_count = 0, edge_count = 0, max_token_len = 0, chunk = 0;
+    uint32_t* d_root_lut = nullptr;
+    uint2* d_trans = nullptr;
+    uint32_t trans_mask = 0;
+    uint32_t* d_node_tok = nullptr;
+    // pooled work buffers (grown on demand, as tokenizer.js:108-166 does)
+    uint8_t* d_in = nullptr; uint64_t in_cap = 0;
+    uint32_t* d_staging = nullptr; uint64_t staging_cap = 0;   // elements
+    uint32_t* d_counts = nullptr; uint64_t counts_cap = 0;
+    uint64_t* d_chunk_off = nullptr; uint64_t chunk_off_cap = 0;
+    uint32_t* d_out = nullptr; uint64_t out_cap = 0;           // elements
+    uint64_t* d_doc_off = nullptr; uint64_t doc_off_cap = 0;
+    uint64_t* d_chunk_base = nullptr; uint64_t chunk_base_cap = 0;
+    uint64_t* d_tok_off = nullptr; uint64_t tok_off_cap = 0;
+    unsigned long long* d_desc = nullptr; uint64_t desc_cap = 0;
+    uint32_t* d_ctl = nullptr;
+    uint64_t* d_total = nullptr;
+    uint64_t* h_total = nullptr;  // pinned: total, error flag
+    cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
+    double walk_ms = 0, compact_ms = 0;
+
+    ~Tokenizer() {
+        if (ctx) cudaSetDevice(ctx->device);
+        cudaFree(d_root_lut); cudaFree(d_trans); cudaFree(d_node_tok); cudaFree(d_in); cudaFree(d_staging);
+        cudaFree(d_counts); cudaFree(d_chunk_off); cudaFree(d_out); cudaFree(d_doc_off); cudaFree(d_chunk_base);
+        cudaFree(d_tok_off); cudaFree(d_desc); cudaFree(d_ctl); cudaFree(d_total);
+        if (h_total) cudaFreeHost(h_total);
+        for (auto e : ev) if (e) cudaEventDestroy(e);
+    }
+
+    template <typename T>
+    b200bpe_status ensure(T** p, uint64_t* cap, uint64_t need, bool grow = true) {
+        if (need <= *cap) return B200BPE_OK;
+        B2_CUDA(cudaStreamSynchronize(ctx->stream));
+        cudaFree(*p);
+        *p = nullptr;
+        const uint64_t want = grow ? need + need / 2 : need;
+        if (cudaMalloc(p, want * sizeof(T)) != cudaSuccess) {
+            cudaGetLastError();
+            B2_CUDA(cudaMalloc(p, need * sizeof(T)));
+            *cap = need;
+        } else {
+            *cap = want;
+        }
+        return B200BPE_OK;
+    }
+
+    b200bpe_status ensure_work(uint64_t max_chunks) {
+        b200bpe_status r;
+        if ((r = ensure(&d_staging, &staging_cap, max_chunks * chunk))) return r;
+        if ((r = ensure(&d_counts, &counts_cap, max_chunks + 1))) return r;
+        if ((r = ensure(&d_chunk_off, &chunk_off_cap, max_chunks + 1))) return r;
+        if ((r = ensure(&d_desc, &desc_cap, max_chunks / SC_THREADS + 2))) return r;
+        return B200BPE_OK;
+    }
+
+    // Walk + scan/compact on device-resident inputs.  d_docs == nullptr → one buffer.
+    b200bpe_status launch(const uint8_t* d_bytes, uint64_t n, const uint64_t* d_docs, uint32_t n_docs,
+                          uint32_t* d_tokens, uint64_t cap, uint64_t* d_tok_offsets) {
+        cudaStream_t s = ctx->stream;
+        const uint64_t max_chunks = (n + chunk - 1) / chunk + (d_docs ? n_docs : 0);
+        b200bpe_status r = ensure_work(std::max<uint64_t>(1, max_chunks));
+        if (r) return r;
+        const uint64_t ntiles = max_chunks / SC_THREADS + 2;
+        B2_CUDA(cudaMemsetAsync(d_desc, 0, ntiles * 8, s));
+        B2_CUDA(cudaMemsetAsync(d_ctl, 0, 8, s));
+        const uint64_t* cb = nullptr;
+        if (d_docs) {
+            if ((r = ensure(&d_chunk_base, &chunk_base_cap, (uint64_t)n_docs + 1))) return r;
+            k_doc_chunk_scan<<<1, 1024, 0, s>>>(d_docs, n_docs, chunk, d_chunk_base);
+            cb = d_chunk_base;
+        }
+        TrieDev t{d_root_lut, d_trans, trans_mask, d_node_tok};
+        const size_t smem = (size_t)(1 << TW_CACHE_LOG2) * 8 + 1024;
+        const int grid_w = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)ctx->sm_count * 3, (max_chunks + TW_THREADS - 1) / TW_THREADS));
+        B2_CUDA(cudaEventRecord(ev[0], s));
+        k_trie_walk<TW_THREADS, TW_CACHE_LOG2><<<grid_w, TW_THREADS, smem, s>>>(
+            t, d_bytes, n, chunk, d_docs, cb, n_docs, (n + chunk - 1) / chunk, d_staging, d_counts);
+        B2_CUDA(cudaEventRecord(ev[1], s));
+        const int grid_c = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)ctx->sm_count * 8, ntiles));
+        k_scan_compact<<<grid_c, SC_THREADS, 0, s>>>(d_staging, d_counts, chunk, cb, n_docs, (n + chunk - 1) / chunk, d_desc,
+                                                    d_ctl, d_chunk_off, d_tokens, cap, d_total);
+        B2_CUDA(cudaEventRecord(ev[2], s));
+        if (d_docs && d_tok_offsets)
+            k_doc_token_offsets<<<std::max(1u, std::min(1024u, (n_docs + 256) / 256)), 256, 0, s>>>(cb, d_chunk_off, n_docs, d_tok_offsets);
+        B2_CUDA(cudaMemcpyAsync(h_total, d_total, 8, cudaMemcpyDeviceToHost, s));
+        B2_CUDA(cudaMemcpyAsync(h_total + 1, d_ctl, 8, cudaMemcpyDeviceToHost, s));
+        B2_CUDA(cudaGetLastError());
+        return B200BPE_OK;
+    }
+
+    b200bpe_status finish(uint64_t cap, uint64_t* n_tokens) {
+        B2_CUDA(cudaStreamSynchronize(ctx->stream));
+        float a = 0, b = 0;
+        cudaEventElapsedTime(&a, ev[0], ev[1]);
+        cudaEventElapsedTime(&b, ev[1], ev[2]);
+        walk_ms = a; compact_ms = b;
+        if ((uint32_t)(h_total[1] >> 32) != 0u) return B200BPE_ERR_LOOKBACK_TIMEOUT;
+        if (n_tokens) *n_tokens = h_total[0];
+        return h_total[0] > cap ? B200BPE_ERR_CAPACITY : B200BPE_OK;
+    }
+};
+
+}  // namespace b200bpe
+
+struct b200bpe_tok { b200bpe::Tokenizer* t; };
+
+using namespace b200bpe;
+
+extern "C" {
+
+b200bpe_status b200bpe_tokenizer_create(b200bpe_ctx* c, const void* trie, size_t len, uint32_t chunk_size,
+                                        b200bpe_tok** out) {
+    if (!c || !trie || !out) return B200BPE_ERR_BAD_ARG;
+    uint32_t f[5];
+    b200bpe_status r = b200bpe_trie_parse_header(trie, len, f);
+    if (r) return r;
+    const uint32_t version = f[0], node_count = f[1], edge_count = f[2], max_len = f[3];
+    if (node_count == 0 || node_count > T_INDEX >> 8) return B200BPE_ERR_BAD_ARG;  // parent index must fit 22 bits + byte
+    const uint8_t* base = static_cast<const uint8_t*>(trie) + 28;
+    // unpack nodes / edges (v3: trie.js:209-249; v2 is the 16-bit legacy layout, parse-only in the reference)
+    std::vector<uint32_t> nodes((size_t)node_count * 3), esym(edge_count), etgt(edge_count);
+    if (version == 3) {
+        std::memcpy(nodes.data(), base, (size_t)node_count * 12);
+        const uint8_t* eb = base + (size_t)node_count * 12;
+        for (uint32_t e = 0; e < edge_count; e++) {
+            esym[e] = eb[(size_t)e * 8];
+            std::memcpy(&etgt[e], eb + (size_t)e * 8 + 4, 4);
+        }
+    } else {
+        for (uint32_t i = 0; i < node_count; i++) {
+            uint16_t h[3];
+            std::memcpy(h, base + (size_t)i * 8, 6);
+            nodes[i * 3] = h[0]; nodes[i * 3 + 1] = h[1]; nodes[i * 3 + 2] = h[2] == 0xFFFF ? INVALID_TOKEN : h[2];
+        }
+        const uint8_t* eb = base + (size_t)node_count * 8;
+        for (uint32_t e = 0; e < edge_count; e++) {
+            uint16_t h[2];
+            std::memcpy(h, eb + (size_t)e * 4, 4);
+            esym[e] = h[0] & 0xFF; etgt[e] = h[1];
+        }
+    }
+    auto packed = [&](uint32_t child) -> uint32_t {
+        uint32_t v = child;
+        if (nodes[(size_t)child * 3 + 2] != INVALID_TOKEN) v |= T_HAS_TOKEN;
+        if ((nodes[(size_t)child * 3 + 1] & 0xFFFFu) == 0) v |= T_LEAF;
+        return v;
+    };
+    uint32_t tlog = 4;
+    while ((1ull << tlog) < (uint64_t)edge_count * 2 + 16) tlog++;
+    std::vector<uint2> trans((size_t)1 << tlog, make_uint2(T_EMPTY_KEY, 0u));
+    std::vector<uint32_t> lut(256, T_MISS), ntok(node_count);
+    const uint32_t tmask = (1u << tlog) - 1;
+    for (uint32_t i = 0; i < node_count; i++) {
+        ntok[i] = nodes[(size_t)i * 3 + 2];
+        const uint32_t fc = nodes[(size_t)i * 3], nc = nodes[(size_t)i * 3 + 1] & 0xFFFFu;  // tokenize.wgsl:102,115
+        for (uint32_t e = fc; e < fc + nc; e++) {
+            if (e >= edge_count || etgt[e] >= node_count) return B200BPE_ERR_TRUNCATED_TRIE;
+            const uint32_t sym = esym[e] & 0xFFu, key = (i << 8) | sym;
+            if (i == 0) { if (lut[sym] == T_MISS) lut[sym] = packed(etgt[e]); continue; }
+            uint32_t slot = (hash_edge_host(key) >> 7) & tmask;
+            bool dup = false;
+            while (trans[slot].x != T_EMPTY_KEY) {
+                if (trans[slot].x == key) { dup = true; break; }  // the binary search finds the first of equal symbols
+                slot = (slot + 1) & tmask;
+            }
+            if (!dup) trans[slot] = make_uint2(key, packed(etgt[e]));
+        }
+    }
+    B2_CUDA(cudaSetDevice(c->c.device));
+    Tokenizer* t = new Tokenizer();
+    t->ctx = &c->c;
+    t->node_count = node_count; t->edge_count = edge_count; t->max_token_len = max_len;
+    t->chunk = chunk_size ? chunk_size : std::max(512u, std::min(2048u, max_len * 8u));  // tokenizer.js:67-68
+    t->trans_mask = tmask;
+    cudaStream_t s = c->c.stream;
+    auto fail = [&](b200bpe_status st) { delete t; return st; };
+#define B2_TRY(expr) if ((expr) != cudaSuccess) { set_last_error(std::string(#expr) + ": " + cudaGetErrorString(cudaGetLastError())); return fail(B200BPE_ERR_CUDA); }
+    B2_TRY(cudaMalloc(&t->d_root_lut, 1024));
+    B2_TRY(cudaMalloc(&t->d_trans, trans.size() * 8));
+    B2_TRY(cudaMalloc(&t->d_node_tok, (size_t)node_count * 4));
+    B2_TRY(cudaMalloc(&t->d_ctl, 8));
+    B2_TRY(cudaMalloc(&t->d_total, 8));
+    B2_TRY(cudaMallocHost(&t->h_total, 16));
+    B2_TRY(cudaMemcpyAsync(t->d_root_lut, lut.data(), 1024, cudaMemcpyHostToDevice, s));
+    B2_TRY(cudaMemcpyAsync(t->d_trans, trans.data(), trans.size() * 8, cudaMemcpyHostToDevice, s));
+    B2_TRY(cudaMemcpyAsync(t->d_node_tok, ntok.data(), (size_t)node_count * 4, cudaMemcpyHostToDevice, s));
+    for (auto& e : t->ev) B2_TRY(cudaEventCreate(&e));
+    B2_TRY(cudaFuncSetAttribute(k_trie_walk<TW_THREADS, TW_CACHE_LOG2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (1 << TW_CACHE_LOG2) * 8 + 1024));
+    // Keep the transition table resident in L2: a persisting access-policy window on the stream.
+    {
+        int max_win = 0;
+        cudaDeviceGetAttribute(&max_win, cudaDevAttrMaxAccessPolicyWindowSize, c->c.device);
+        const size_t bytes = std::min<size_t>(trans.size() * 8, (size_t)std::max(0, max_win));
+        if (bytes > 0) {
+            cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, std::min<size_t>(bytes, 32u << 20));
+            cudaStreamAttrValue attr{};
+            attr.accessPolicyWindow.base_ptr = t->d_trans;
+            attr.accessPolicyWindow.num_bytes = bytes;
+            attr.accessPolicyWindow.hitRatio = 1.0f;
+            attr.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
+            attr.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
+            cudaStreamSetAttribute(s, cudaStreamAttributeAccessPolicyWindow, &attr);
+            cudaGetLastError();
+        }
+    }
+    B2_TRY(cudaStreamSynchronize(s));
+#undef B2_TRY
+    *out = new b200bpe_tok{t};
+    return B200BPE_OK;
+}
+
+b200bpe_status b200bpe_tokenizer_info(b200bpe_tok* h, uint32_t* node_count, uint32_t* edge_count,
+                                      uint32_t* max_token_len, uint32_t* chunk_size) {
+    if (!h) return B200BPE_ERR_BAD_ARG;
+    if (node_count) *node_count = h->t->node_count;
+    if (edge_count) *edge_count = h->t->edge_count;
+    if (max_token_len) *max_token_len = h->t->max_token_len;
+    if (chunk_size) *chunk_size = h->t->chunk;
+    return B200BPE_OK;
+}
+
+b200bpe_status b200bpe_encode_device(b200bpe_tok* h, const uint8_t* d_bytes, uint64_t n, uint32_t* d_tokens_out,
+                                     uint64_t cap, uint64_t* n_tokens_out) {
+    if (!h || (!d_bytes && n) || (!d_tokens_out && cap)) return B200BPE_ERR_BAD_ARG;
+    Tokenizer* t = h->t;
+    B2_CUDA(cudaSetDevice(t->ctx->device));
+    if (n == 0) { if (n_tokens_out) *n_tokens_out = 0; return B200BPE_OK; }
+    b200bpe_status r = t->launch(d_bytes, n, nullptr, 0, d_tokens_out, cap, nullptr);
+    if (r) return r;
+    return t->finish(cap, n_tokens_out);
+}
+
+b200bpe_status b200bpe_encode_batch_device(b200bpe_tok* h, const uint8_t* d_bytes, const uint64_t* d_doc_offsets,
+                                           uint32_t n_docs, uint64_t n_bytes, uint32_t* d_tokens_out, uint64_t cap,
+                                           uint64_t* d_tok_offsets_out, uint64_t* n_tokens_out) {
+    if (!h || !d_doc_offsets || (!d_bytes && n_bytes) || (!d_tokens_out && cap)) return B200BPE_ERR_BAD_ARG;
+    Tokenizer* t = h->t;
+    B2_CUDA(cudaSetDevice(t->ctx->device));
+    b200bpe_status r = t->launch(d_bytes, n_bytes, d_doc_offsets, n_docs, d_tokens_out, cap, d_tok_offsets_out);
+    if (r) return r;
+    return t->finish(cap, n_tokens_out);
+}
+
+// encodeBytes: upload, encode, read the total, then read back exactly total*4 bytes
+// (tokenizer.js:226-233,312-334).
+b200bpe_status b200bpe_encode(b200bpe_tok* h, const uint8_t* bytes, uint64_t n, uint32_t* tokens_out, uint64_t cap,
+                              uint64_t* n_tokens_out) {
+    if (!h || (!bytes && n) || !n_tokens_out) return B200BPE_ERR_BAD_ARG;
+    Tokenizer* t = h->t;
+    *n_tokens_out = 0;
+    if (n == 0) return B200BPE_OK;
+    B2_CUDA(cudaSetDevice(t->ctx->device));
+    cudaStream_t s = t->ctx->stream;
+    // Inputs beyond 8 GiB go through in chunk-aligned slices, as tokenizer.js:181-203 slices to its
+    // buffer limit; the result is the same as one pass because slices end on chunk boundaries.
+    const uint64_t slice = ((8ull << 30) / t->chunk) * t->chunk;
+    uint64_t done_tokens = 0;
+    for (uint64_t off = 0; off < n; off += slice) {
+        const uint64_t m = std::min(slice, n - off);
+        b200bpe_status r;
+        if ((r = t->ensure(&t->d_in, &t->in_cap, m + 16))) return r;
+        if ((r = t->ensure(&t->d_out, &t->out_cap, m))) return r;  // worst case: one token per byte
+        B2_CUDA(cudaMemcpyAsync(t->d_in, bytes + off, m, cudaMemcpyHostToDevice, s));
+        if ((r = t->launch(t->d_in, m, nullptr, 0, t->d_out, t->out_cap, nullptr))) return r;
+        uint64_t got = 0;
+        if ((r = t->finish(t->out_cap, &got))) return r;
+        if (done_tokens + got > cap || !tokens_out) { *n_tokens_out = done_tokens + got; return B200BPE_ERR_CAPACITY; }
+        B2_CUDA(cudaMemcpyAsync(tokens_out + done_tokens, t->d_out, got * 4, cudaMemcpyDeviceToHost, s));
+        B2_CUDA(cudaStreamSynchronize(s));
+        done_tokens += got;
+    }
+    *n_tokens_out = done_tokens;
+    return B200BPE_OK;
+}
+
+b200bpe_status b200bpe_encode_batch(b200bpe_tok* h, const uint8_t* bytes, const uint64_t* doc_offsets, uint32_t n_docs,
+                                    uint32_t* tokens_out, uint64_t cap, uint64_t* tok_offsets_out) {
+    if (!h || !doc_offsets || !tok_offsets_out) return B200BPE_ERR_BAD_ARG;
+    Tokenizer* t = h->t;
+    B2_CUDA(cudaSetDevice(t->ctx->device));
+    cudaStream_t s = t->ctx->stream;
+    const uint64_t n = doc_offsets[n_docs] - doc_offsets[0];
+    for (uint32_t d = 0; d < n_docs; d++) if (doc_offsets[d + 1] < doc_offsets[d]) return B200BPE_ERR_BAD_ARG;
+    b200bpe_status r;
+    if ((r = t->ensure(&t->d_in, &t->in_cap, n + 16))) return r;
+    if ((r = t->ensure(&t->d_out, &t->out_cap, std::max<uint64_t>(1, n)))) return r;
+    if ((r = t->ensure(&t->d_doc_off, &t->doc_off_cap, (uint64_t)n_docs + 1))) return r;
+    if ((r = t->ensure(&t->d_tok_off, &t->tok_off_cap, (uint64_t)n_docs + 1))) return r;
+    // offsets relative to the first document, so the device buffer starts at 0
+    std::vector<uint64_t> rel((size_t)n_docs + 1);
+    for (uint32_t d = 0; d <= n_docs; d++) rel[d] = doc_offsets[d] - doc_offsets[0];
+    if (n) B2_CUDA(cudaMemcpyAsync(t->d_in, bytes + doc_offsets[0], n, cudaMemcpyHostToDevice, s));
+    B2_CUDA(cudaMemcpyAsync(t->d_doc_off, rel.data(), ((size_t)n_docs + 1) * 8, cudaMemcpyHostToDevice, s));
+    if ((r = t->launch(t->d_in, n, t->d_doc_off, n_docs, t->d_out, t->out_cap, t->d_tok_off))) return r;
+    uint64_t got = 0;
+    if ((r = t->finish(t->out_cap, &got))) return r;
+    B2_CUDA(cudaMemcpyAsync(tok_offsets_out, t->d_tok_off, ((size_t)n_docs + 1) * 8, cudaMemcpyDeviceToHost, s));
+    if (got > cap || (!tokens_out && got)) { cudaStreamSynchronize(s); return B200BPE_ERR_CAPACITY; }
+    if (got) B2_CUDA(cudaMemcpyAsync(tokens_out, t->d_out, got * 4, cudaMemcpyDeviceToHost, s));
+    B2_CUDA(cudaStreamSynchronize(s));
+    return B200BPE_OK;
+}
+
+b200bpe_status b200bpe_tokenizer_last_ms(b200bpe_tok* h, double* walk_ms, double* compact_ms) {
+    if (!h) return B200BPE_ERR_BAD_ARG;
+    if (walk_ms) *walk_ms = h->t->walk_ms;
+    if (compact_ms) *compact_ms = h->t->compact_ms;
+    return B200BPE_OK;
+}
+
+void b200bpe_tokenizer_destroy(b200bpe_tok* h) {
+    if (!h) return;
+    delete h->t;
+    delete h;
+}
+
+}  // extern "C"

@@ -1,0 +1,520 @@
+// Host side of the training path: device buffers, the per-batch CUDA graph, the batch loop
+// that mirrors BPETrainer.#runTrainingLoop (src/bpe/trainer.js:225-335 of the reference), and
+// the C entry points declared in include/b200bpe.h.
+#include <algorithm>
+#include <chrono>
+#include <cstring>
+#include <vector>
+
+#include "ctx.cuh"
+#include "train_kernels.cuh"
+#include "exchange_kernels.cuh"
+
+namespace b200bpe {
+
+namespace {
+
+constexpr uint32_t MAX_TABLE_LOG2 = 27;
+
+uint32_t ceil_log2(uint64_t x) {
+    uint32_t l = 0;
+    while ((1ull << l) < x) l++;
+    return l;
+}
+
+}  // namespace
+
+struct Trainer {
+    Ctx* ctx = nullptr;
+    uint64_t n0 = 0;            // symbols at creation (this rank)
+    b200bpe_train_opts opts{};
+    uint32_t merges_goal = 0;   // target_vocab_size - first_token_id
+    // resident inputs, to rebuild the symbols on reset
+    uint8_t* d_bytes = nullptr;
+    uint8_t* d_mask = nullptr;
+    uint32_t* d_sym_init = nullptr;
+    bool own_inputs = true;
+    bool has_mask = false;
+    // working set
+    uint32_t* buf[2] = {nullptr, nullptr};
+    uint64_t cap_elems = 0;
+    PairSlot* table = nullptr;
+    uint32_t table_log2 = 0;
+    DevState* d_state = nullptr;
+    DevState* h_state = nullptr;  // pinned
+    uint32_t* d_log = nullptr;
+    uint32_t* h_log = nullptr;    // pinned
+    CtaBest* d_cta_best = nullptr;
+    unsigned long long* d_desc = nullptr;
+    Exchange xch;                 // sharded runs only
+    cudaGraphExec_t graph = nullptr;
+    uint32_t graph_iters = 0;
+    int grid_pc = 1, grid_am = 1, grid_mc = 1;
+    // host mirror
+    uint32_t merges_done = 0;
+    bool early_stop = false;
+    uint64_t cur_n = 0;
+    // timing
+    cudaEvent_t ev_run0 = nullptr, ev_run1 = nullptr;
+    double last_run_ms = 0;
+    std::vector<cudaEvent_t> kev;
+    b200bpe_kernel_stats stats{};
+
+    ~Trainer();
+    b200bpe_status alloc_common();
+    b200bpe_status init_state();
+    b200bpe_status build_graph();
+    b200bpe_status enqueue_merge(int iter, bool timed);
+    b200bpe_status grow_table();
+    b200bpe_status run(uint32_t max_merges, uint32_t* merges_out, uint32_t* counts_out, uint32_t* n_out,
+                       uint32_t* early_out, b200bpe_progress_cb cb, void* user);
+};
+
+Trainer::~Trainer() {
+    if (ctx) cudaSetDevice(ctx->device);
+    if (graph) cudaGraphExecDestroy(graph);
+    if (own_inputs) { cudaFree(d_bytes); cudaFree(d_mask); }
+    cudaFree(d_sym_init);
+    cudaFree(buf[0]); cudaFree(buf[1]); cudaFree(table); cudaFree(d_state); cudaFree(d_log);
+    cudaFree(d_cta_best); cudaFree(d_desc);
+    xch.release();
+    if (h_state) cudaFreeHost(h_state);
+    if (h_log) cudaFreeHost(h_log);
+    if (ev_run0) cudaEventDestroy(ev_run0);
+    if (ev_run1) cudaEventDestroy(ev_run1);
+    for (auto e : kev) cudaEventDestroy(e);
+}
+
+b200bpe_status Trainer::alloc_common() {
+    cap_elems = ((n0 + 3) & ~3ull) + 8;
+    B2_CUDA(cudaMalloc(&buf[0], cap_elems * 4));
+    B2_CUDA(cudaMalloc(&buf[1], cap_elems * 4));
+    table_log2 = opts.table_log2;
+    if (table_log2 == 0) table_log2 = std::min<uint32_t>(21, std::max<uint32_t>(15, ceil_log2(n0 / 8 + 1)));
+    table_log2 = std::min(table_log2, MAX_TABLE_LOG2);
+    B2_CUDA(cudaMalloc(&table, sizeof(PairSlot) << table_log2));
+    B2_CUDA(cudaMalloc(&d_state, sizeof(DevState)));
+    B2_CUDA(cudaMallocHost(&h_state, sizeof(DevState)));
+    const size_t log_bytes = (size_t)std::max<uint32_t>(1, merges_goal) * 16;
+    B2_CUDA(cudaMalloc(&d_log, log_bytes));
+    B2_CUDA(cudaMallocHost(&h_log, log_bytes));
+    const int sms = ctx->sm_count;
+    const uint64_t nvec = (n0 + 3) / 4;
+    grid_pc = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)sms * 2, (nvec + PC_THREADS - 1) / PC_THREADS));
+    grid_am = std::max(1, std::min(sms * 4, (int)((1u << table_log2) / (AM_THREADS * 4))));
+    const uint64_t ntiles = (n0 + MC_TILE - 1) / MC_TILE;
+    grid_mc = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)sms * 8, ntiles));
+    B2_CUDA(cudaMalloc(&d_cta_best, sizeof(CtaBest) * (size_t)(sms * 4 + 1)));
+    B2_CUDA(cudaMalloc(&d_desc, sizeof(unsigned long long) * (ntiles + 1)));
+    B2_CUDA(cudaMemsetAsync(d_desc, 0, sizeof(unsigned long long) * (ntiles + 1), ctx->stream));
+    B2_CUDA(cudaEventCreate(&ev_run0));
+    B2_CUDA(cudaEventCreate(&ev_run1));
+    B2_CUDA(cudaFuncSetAttribute(k_pair_count<PC_SLOTS_LOG2, PC_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (1 << PC_SLOTS_LOG2) * 12));
+    if (ctx->world > 1) {
+        b200bpe_status s = xch.init(ctx, table_log2);
+        if (s) return s;
+    }
+    return B200BPE_OK;
+}
+
+// Rebuild the tagged symbols from the resident inputs and put the control block back to the
+// state of a fresh BPETrainer.train call (trainer.js:187-196).
+b200bpe_status Trainer::init_state() {
+    cudaStream_t s = ctx->stream;
+    if (d_sym_init) {
+        B2_CUDA(cudaMemcpyAsync(buf[0], d_sym_init, n0 * 4, cudaMemcpyDeviceToDevice, s));
+    } else {
+        const int grid = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)ctx->sm_count * 8, (n0 + 255) / 256));
+        k_tag_symbols<<<grid, 256, 0, s>>>(d_bytes, has_mask ? d_mask : nullptr, buf[0], n0);
+    }
+    if (cap_elems > n0) B2_CUDA(cudaMemsetAsync(buf[0] + n0, 0, (cap_elems - n0) * 4, s));
+    // The destination buffer starts zeroed, as a fresh WebGPU buffer does; in literal mode its
+    // untouched tail is observable.
+    B2_CUDA(cudaMemsetAsync(buf[1], 0, cap_elems * 4, s));
+    B2_CUDA(cudaMemsetAsync(table, 0, sizeof(PairSlot) << table_log2, s));
+    std::memset(h_state, 0, sizeof(DevState));
+    h_state->n[0] = (uint32_t)n0;
+    h_state->next_id = opts.first_token_id;
+    h_state->table_log2 = table_log2;
+    h_state->literal = (opts.compat_mode == B200BPE_COMPAT_LITERAL) ? 1u : 0u;
+    h_state->world = (uint32_t)ctx->world;
+    B2_CUDA(cudaMemcpyAsync(d_state, h_state, sizeof(DevState), cudaMemcpyHostToDevice, s));
+    B2_CUDA(cudaStreamSynchronize(s));
+    merges_done = 0;
+    early_stop = false;
+    cur_n = n0;
+    std::memset(&stats, 0, sizeof(stats));
+    return B200BPE_OK;
+}
+
+__global__ void k_begin_batch(DevState* st, uint32_t target) {
+    st->merges_target = target;
+    st->target_hit = (st->merges_done >= target) ? 1u : 0u;
+}
+__global__ void k_clear_status(DevState* st, uint32_t table_log2) {
+    st->status = DS_OK;
+    st->want_grow = 0u;
+    st->table_log2 = table_log2;
+}
+
+// One merge iteration on the stream.  `timed` brackets each kernel with events.
+b200bpe_status Trainer::enqueue_merge(int iter, bool timed) {
+    cudaStream_t s = ctx->stream;
+    const bool literal = opts.compat_mode == B200BPE_COMPAT_LITERAL;
+    auto ev = [&](int k) -> cudaError_t {
+        return timed ? cudaEventRecord(kev[(size_t)iter * 8 + k], s) : cudaSuccess;
+    };
+    B2_CUDA(ev(0));
+    k_pair_count<PC_SLOTS_LOG2, PC_THREADS><<<grid_pc, PC_THREADS, (1 << PC_SLOTS_LOG2) * 12, s>>>(d_state, buf[0], buf[1], table);
+    B2_CUDA(ev(1));
+    if (ctx->world > 1) {
+        b200bpe_status r = xch.enqueue(ctx, d_state, table, table_log2, d_cta_best, d_log, grid_am);
+        if (r) return r;
+        B2_CUDA(ev(2));
+    } else {
+        B2_CUDA(ev(2));
+        k_argmax_setup<<<grid_am, AM_THREADS, 0, s>>>(d_state, table, d_cta_best, d_log, 0);
+    }
+    B2_CUDA(ev(3));
+    if (literal) k_merge_compact<true><<<grid_mc, MC_THREADS, 0, s>>>(d_state, buf[0], buf[1], d_desc);
+    else k_merge_compact<false><<<grid_mc, MC_THREADS, 0, s>>>(d_state, buf[0], buf[1], d_desc);
+    B2_CUDA(ev(4));
+    B2_CUDA(cudaGetLastError());
+    return B200BPE_OK;
+}
+
+b200bpe_status Trainer::build_graph() {
+    if (graph) { cudaGraphExecDestroy(graph); graph = nullptr; }
+    cudaStream_t s = ctx->stream;
+    cudaGraph_t g = nullptr;
+    B2_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    b200bpe_status r = B200BPE_OK;
+    for (uint32_t i = 0; i < opts.batch_merges && r == B200BPE_OK; i++) r = enqueue_merge((int)i, false);
+    cudaError_t e = cudaStreamEndCapture(s, &g);
+    if (r != B200BPE_OK) { if (g) cudaGraphDestroy(g); return r; }
+    B2_CUDA(e);
+    e = cudaGraphInstantiate(&graph, g, 0);
+    cudaGraphDestroy(g);
+    B2_CUDA(e);
+    graph_iters = opts.batch_merges;
+    return B200BPE_OK;
+}
+
+b200bpe_status Trainer::grow_table() {
+    if (table_log2 >= MAX_TABLE_LOG2) return B200BPE_ERR_TABLE_FULL;
+    cudaStream_t s = ctx->stream;
+    B2_CUDA(cudaStreamSynchronize(s));
+    B2_CUDA(cudaFree(table));
+    table = nullptr;
+    table_log2++;
+    B2_CUDA(cudaMalloc(&table, sizeof(PairSlot) << table_log2));
+    B2_CUDA(cudaMemsetAsync(table, 0, sizeof(PairSlot) << table_log2, s));
+    grid_am = std::max(1, std::min(ctx->sm_count * 4, (int)((1u << table_log2) / (AM_THREADS * 4))));
+    if (ctx->world > 1) {
+        b200bpe_status r = xch.resize(ctx, table_log2);
+        if (r) return r;
+    }
+    k_clear_status<<<1, 1, 0, s>>>(d_state, table_log2);
+    if (graph) { cudaGraphExecDestroy(graph); graph = nullptr; }
+    return B200BPE_OK;
+}
+
+b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t* counts_out, uint32_t* n_out,
+                            uint32_t* early_out, b200bpe_progress_cb cb, void* user) {
+    B2_CUDA(cudaSetDevice(ctx->device));
+    cudaStream_t s = ctx->stream;
+    const bool timed = (opts.flags & B200BPE_FLAG_TIME_KERNELS) != 0;
+    const bool use_graph = !timed && !(opts.flags & B200BPE_FLAG_NO_GRAPH);
+    uint32_t remaining = merges_goal - merges_done;
+    if (max_merges && max_merges < remaining) remaining = max_merges;
+    const uint32_t start_done = merges_done;
+    if (timed && kev.empty()) {
+        kev.resize((size_t)opts.batch_merges * 8);
+        for (auto& e : kev) B2_CUDA(cudaEventCreate(&e));
+    }
+    auto t0 = std::chrono::steady_clock::now();
+    B2_CUDA(cudaEventRecord(ev_run0, s));
+    int grow_retries = 0;
+    while (remaining > 0 && !early_stop) {
+        const uint32_t batch = std::min(opts.batch_merges, remaining);
+        const uint32_t before = merges_done;
+        k_begin_batch<<<1, 1, 0, s>>>(d_state, before + batch);
+        if (use_graph) {
+            if (!graph) { b200bpe_status r = build_graph(); if (r) return r; }
+            B2_CUDA(cudaGraphLaunch(graph, s));
+        } else {
+            for (uint32_t i = 0; i < batch; i++) { b200bpe_status r = enqueue_merge((int)i, timed); if (r) return r; }
+        }
+        // One read-back per batch: the control block and this batch's slice of the merge log
+        // (trainer.js:248-267 reads the same two things).
+        B2_CUDA(cudaMemcpyAsync(h_state, d_state, sizeof(DevState), cudaMemcpyDeviceToHost, s));
+        B2_CUDA(cudaMemcpyAsync(h_log + (size_t)before * 4, d_log + (size_t)before * 4, (size_t)batch * 16,
+                                cudaMemcpyDeviceToHost, s));
+        B2_CUDA(cudaStreamSynchronize(s));
+        const uint32_t done_now = h_state->merges_done;
+        const uint32_t got = done_now - before;
+        if (timed) {
+            uint64_t nk = cur_n;
+            for (uint32_t i = 0; i < batch; i++) {
+                float ms = 0;
+                const size_t b = (size_t)i * 8;
+                const bool merged = i < got;
+                cudaEventElapsedTime(&ms, kev[b + 0], kev[b + 1]); stats.pair_count_ms += ms;
+                cudaEventElapsedTime(&ms, kev[b + 1], kev[b + 2]); stats.exchange_ms += ms;
+                cudaEventElapsedTime(&ms, kev[b + 2], kev[b + 3]); stats.argmax_ms += ms;
+                cudaEventElapsedTime(&ms, kev[b + 3], kev[b + 4]); stats.merge_compact_ms += ms;
+                stats.pair_count_launches++; stats.argmax_launches++; stats.merge_compact_launches++;
+                if (ctx->world > 1) stats.exchange_launches++;
+                stats.pair_count_bytes += 4ull * nk;
+                stats.argmax_bytes += 24ull << table_log2;
+                if (merged) {
+                    const uint64_t nn = (ctx->world > 1) ? nk : nk - h_log[(size_t)(before + i) * 4 + 3];
+                    stats.merge_compact_bytes += 4ull * nk + 4ull * nn;
+                    nk = nn;
+                }
+            }
+        }
+        for (uint32_t i = 0; i < got; i++) {
+            const uint32_t* l = h_log + (size_t)(before + i) * 4;
+            const size_t o = (size_t)(before + i - start_done);
+            if (merges_out) { merges_out[o * 3 + 0] = l[0]; merges_out[o * 3 + 1] = l[1]; merges_out[o * 3 + 2] = l[2]; }
+            if (counts_out) counts_out[o] = l[3];
+        }
+        merges_done = done_now;
+        remaining -= got;
+        cur_n = h_state->n[h_state->epoch & 1];
+        early_stop = h_state->early_stop != 0;
+        if (h_state->status == DS_TABLE_FULL || h_state->want_grow) {
+            const bool was_full = h_state->status == DS_TABLE_FULL;
+            b200bpe_status r = grow_table();
+            if (r) return r;
+            if (was_full && ++grow_retries > 16) return B200BPE_ERR_TABLE_FULL;
+        } else if (h_state->status == DS_LOOKBACK_TIMEOUT) {
+            return B200BPE_ERR_LOOKBACK_TIMEOUT;
+        } else if (h_state->status != DS_OK) {
+            return B200BPE_ERR_INTERNAL;
+        }
+        if (cb) {
+            b200bpe_progress p{};
+            p.merge_index = merges_done;
+            p.total_merges = merges_goal;
+            if (got) {
+                const uint32_t* l = h_log + (size_t)(merges_done - 1) * 4;
+                p.last_a = l[0]; p.last_b = l[1]; p.last_new_id = l[2]; p.last_count = l[3];
+            }
+            p.symbol_count = cur_n;
+            const double el = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+            p.merges_per_second = el > 0 ? (merges_done - start_done) / el : 0.0;
+            cb(&p, user);
+        }
+    }
+    B2_CUDA(cudaEventRecord(ev_run1, s));
+    B2_CUDA(cudaEventSynchronize(ev_run1));
+    float ms = 0;
+    cudaEventElapsedTime(&ms, ev_run0, ev_run1);
+    last_run_ms = ms;
+    if (n_out) *n_out = merges_done - start_done;
+    if (early_out) *early_out = early_stop ? 1u : 0u;
+    return B200BPE_OK;
+}
+
+static b200bpe_status check_opts(const Ctx* ctx, const b200bpe_train_opts* in, b200bpe_train_opts* o) {
+    std::memset(o, 0, sizeof(*o));
+    if (in) {
+        if (in->struct_size != sizeof(b200bpe_train_opts)) return B200BPE_ERR_BAD_ARG;
+        *o = *in;
+    }
+    if (o->target_vocab_size == 0) o->target_vocab_size = 4096;
+    if (o->first_token_id == 0) o->first_token_id = 256;
+    if (o->batch_merges == 0) o->batch_merges = 128;
+    if (o->batch_merges > 4096) return B200BPE_ERR_BAD_ARG;
+    if (o->compat_mode > B200BPE_COMPAT_FIXED) return B200BPE_ERR_BAD_ARG;
+    if (o->target_vocab_size < o->first_token_id) return B200BPE_ERR_BAD_ARG;
+    if (ctx->world > 1 && o->compat_mode != B200BPE_COMPAT_FIXED) return B200BPE_ERR_BAD_ARG;
+    if (o->table_log2 && (o->table_log2 < 4 || o->table_log2 > MAX_TABLE_LOG2)) return B200BPE_ERR_BAD_ARG;
+    return B200BPE_OK;
+}
+
+static b200bpe_status make_trainer(b200bpe_ctx* c, const uint8_t* bytes, const uint8_t* mask, const uint32_t* symbols,
+                                   uint64_t n, bool device_inputs, const b200bpe_train_opts* opts, Trainer** out) {
+    if (!c || !out || (!bytes && !symbols)) return B200BPE_ERR_BAD_ARG;
+    // A shard of a sharded job may be empty; a single-GPU corpus may not (trainer.js:161-163).
+    if (n == 0 && c->c.world == 1) return B200BPE_ERR_EMPTY_CORPUS;
+    if (n >= 0xFFFFFFF0ull) return B200BPE_ERR_BAD_ARG;  // per-GPU symbol indices are 32-bit
+    B2_CUDA(cudaSetDevice(c->c.device));
+    Trainer* t = new Trainer();
+    t->ctx = &c->c;
+    t->n0 = n;
+    b200bpe_status r = check_opts(&c->c, opts, &t->opts);
+    if (r) { delete t; return r; }
+    t->merges_goal = t->opts.target_vocab_size - t->opts.first_token_id;
+    auto fail = [&](b200bpe_status st) { delete t; return st; };
+    cudaStream_t s = c->c.stream;
+    const size_t nb = std::max<uint64_t>(n, 1);
+    if (symbols) {
+        if (cudaMalloc(&t->d_sym_init, nb * 4) != cudaSuccess) return fail(B200BPE_ERR_OOM);
+        if (cudaMemcpyAsync(t->d_sym_init, symbols, n * 4, device_inputs ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, s) != cudaSuccess)
+            return fail(B200BPE_ERR_CUDA);
+    } else if (device_inputs) {
+        t->own_inputs = false;
+        t->d_bytes = const_cast<uint8_t*>(bytes);
+        t->d_mask = const_cast<uint8_t*>(mask);
+        t->has_mask = mask != nullptr;
+    } else {
+        if (cudaMalloc(&t->d_bytes, nb) != cudaSuccess) return fail(B200BPE_ERR_OOM);
+        if (cudaMemcpyAsync(t->d_bytes, bytes, n, cudaMemcpyHostToDevice, s) != cudaSuccess) return fail(B200BPE_ERR_CUDA);
+        if (mask) {
+            if (cudaMalloc(&t->d_mask, nb) != cudaSuccess) return fail(B200BPE_ERR_OOM);
+            if (cudaMemcpyAsync(t->d_mask, mask, n, cudaMemcpyHostToDevice, s) != cudaSuccess) return fail(B200BPE_ERR_CUDA);
+            t->has_mask = true;
+        }
+    }
+    r = t->alloc_common();
+    if (r) return fail(r);
+    r = t->init_state();
+    if (r) return fail(r);
+    *out = t;
+    return B200BPE_OK;
+}
+
+}  // namespace b200bpe
+
+struct b200bpe_trainer { b200bpe::Trainer* t; };
+
+using namespace b200bpe;
+
+static b200bpe_status wrap(Trainer* t, b200bpe_trainer** out) {
+    *out = new b200bpe_trainer{t};
+    return B200BPE_OK;
+}
+
+extern "C" {
+
+b200bpe_status b200bpe_trainer_create(b200bpe_ctx* c, const uint8_t* bytes, const uint8_t* word_starts, uint64_t n,
+                                      const b200bpe_train_opts* opts, b200bpe_trainer** out) {
+    Trainer* t = nullptr;
+    b200bpe_status r = make_trainer(c, bytes, word_starts, nullptr, n, false, opts, &t);
+    return r ? r : wrap(t, out);
+}
+
+b200bpe_status b200bpe_trainer_create_device(b200bpe_ctx* c, const uint8_t* d_bytes, const uint8_t* d_word_starts,
+                                             uint64_t n, const b200bpe_train_opts* opts, b200bpe_trainer** out) {
+    Trainer* t = nullptr;
+    b200bpe_status r = make_trainer(c, d_bytes, d_word_starts, nullptr, n, true, opts, &t);
+    return r ? r : wrap(t, out);
+}
+
+b200bpe_status b200bpe_trainer_create_from_symbols(b200bpe_ctx* c, const uint32_t* symbols, uint64_t n,
+                                                   const b200bpe_train_opts* opts, b200bpe_trainer** out) {
+    Trainer* t = nullptr;
+    b200bpe_status r = make_trainer(c, nullptr, nullptr, symbols, n, false, opts, &t);
+    return r ? r : wrap(t, out);
+}
+
+b200bpe_status b200bpe_trainer_run(b200bpe_trainer* h, uint32_t max_merges, uint32_t* merges_out, uint32_t* counts_out,
+                                   uint32_t* n_merges_out, uint32_t* early_stop_out, b200bpe_progress_cb cb, void* user) {
+    if (!h) return B200BPE_ERR_BAD_ARG;
+    return h->t->run(max_merges, merges_out, counts_out, n_merges_out, early_stop_out, cb, user);
+}
+
+b200bpe_status b200bpe_trainer_reset(b200bpe_trainer* h) {
+    if (!h) return B200BPE_ERR_BAD_ARG;
+    B2_CUDA(cudaSetDevice(h->t->ctx->device));
+    return h->t->init_state();
+}
+
+b200bpe_status b200bpe_trainer_symbols(b200bpe_trainer* h, uint32_t* out, uint64_t cap, uint64_t* n_out) {
+    if (!h || !n_out) return B200BPE_ERR_BAD_ARG;
+    Trainer* t = h->t;
+    B2_CUDA(cudaSetDevice(t->ctx->device));
+    B2_CUDA(cudaMemcpyAsync(t->h_state, t->d_state, sizeof(DevState), cudaMemcpyDeviceToHost, t->ctx->stream));
+    B2_CUDA(cudaStreamSynchronize(t->ctx->stream));
+    const uint32_t e = t->h_state->epoch;
+    const uint64_t n = t->h_state->n[e & 1];
+    *n_out = n;
+    if (!out) return B200BPE_OK;
+    if (cap < n) return B200BPE_ERR_CAPACITY;
+    B2_CUDA(cudaMemcpy(out, t->buf[e & 1], n * 4, cudaMemcpyDeviceToHost));
+    return B200BPE_OK;
+}
+
+b200bpe_status b200bpe_trainer_pair_counts(b200bpe_trainer* h, uint64_t* keys_out, uint32_t* counts_out, uint64_t cap,
+                                           uint64_t* n_distinct_out) {
+    if (!h || !n_distinct_out) return B200BPE_ERR_BAD_ARG;
+    Trainer* t = h->t;
+    B2_CUDA(cudaSetDevice(t->ctx->device));
+    cudaStream_t s = t->ctx->stream;
+    for (int attempt = 0; attempt < 12; attempt++) {
+        k_begin_batch<<<1, 1, 0, s>>>(t->d_state, 0xFFFFFFFFu);
+        k_pair_count<PC_SLOTS_LOG2, PC_THREADS><<<t->grid_pc, PC_THREADS, (1 << PC_SLOTS_LOG2) * 12, s>>>(
+            t->d_state, t->buf[0], t->buf[1], t->table);
+        PairSlot* tab = t->table;
+        uint32_t tl2 = t->table_log2;
+        if (t->ctx->world > 1) {
+            b200bpe_status r = t->xch.enqueue_counts_only(t->ctx, t->d_state, t->table, t->table_log2);
+            if (r) return r;
+            tab = t->xch.owned;
+            tl2 = t->xch.owned_log2;
+        }
+        unsigned long long* dk = nullptr;
+        uint32_t *dc = nullptr, *dn = nullptr;
+        const uint32_t dcap = (uint32_t)std::min<uint64_t>(cap, 1ull << tl2);
+        B2_CUDA(cudaMalloc(&dk, std::max<size_t>(8, (size_t)dcap * 8)));
+        B2_CUDA(cudaMalloc(&dc, std::max<size_t>(4, (size_t)dcap * 4)));
+        B2_CUDA(cudaMalloc(&dn, 4));
+        B2_CUDA(cudaMemsetAsync(dn, 0, 4, s));
+        k_dump_table<<<t->ctx->sm_count * 4, 256, 0, s>>>(tab, 1u << tl2, dk, dc, dcap, dn);
+        if (tab != t->table) B2_CUDA(cudaMemsetAsync(t->table, 0, sizeof(PairSlot) << t->table_log2, s));
+        uint32_t nd = 0;
+        B2_CUDA(cudaMemcpyAsync(&nd, dn, 4, cudaMemcpyDeviceToHost, s));
+        B2_CUDA(cudaMemcpyAsync(t->h_state, t->d_state, sizeof(DevState), cudaMemcpyDeviceToHost, s));
+        B2_CUDA(cudaStreamSynchronize(s));
+        const bool full = t->h_state->status == DS_TABLE_FULL;
+        if (!full) {
+            const uint32_t m = std::min(nd, dcap);
+            if (keys_out) B2_CUDA(cudaMemcpy(keys_out, dk, (size_t)m * 8, cudaMemcpyDeviceToHost));
+            if (counts_out) B2_CUDA(cudaMemcpy(counts_out, dc, (size_t)m * 4, cudaMemcpyDeviceToHost));
+        }
+        cudaFree(dk); cudaFree(dc); cudaFree(dn);
+        if (!full) {
+            *n_distinct_out = nd;
+            return nd > cap ? B200BPE_ERR_CAPACITY : B200BPE_OK;
+        }
+        b200bpe_status r = t->grow_table();
+        if (r) return r;
+    }
+    return B200BPE_ERR_TABLE_FULL;
+}
+
+b200bpe_status b200bpe_trainer_kernel_stats(b200bpe_trainer* h, b200bpe_kernel_stats* out) {
+    if (!h || !out) return B200BPE_ERR_BAD_ARG;
+    *out = h->t->stats;
+    return B200BPE_OK;
+}
+
+b200bpe_status b200bpe_trainer_last_run_ms(b200bpe_trainer* h, double* ms) {
+    if (!h || !ms) return B200BPE_ERR_BAD_ARG;
+    *ms = h->t->last_run_ms;
+    return B200BPE_OK;
+}
+
+void b200bpe_trainer_destroy(b200bpe_trainer* h) {
+    if (!h) return;
+    delete h->t;
+    delete h;
+}
+
+b200bpe_status b200bpe_train(b200bpe_ctx* c, const uint8_t* bytes, const uint8_t* word_starts, uint64_t n,
+                             const b200bpe_train_opts* opts, uint32_t* merges_out, uint32_t* counts_out,
+                             uint32_t* n_merges_out, uint32_t* early_stop_out, b200bpe_progress_cb cb, void* user) {
+    if (!merges_out || !n_merges_out) return B200BPE_ERR_BAD_ARG;
+    b200bpe_trainer* h = nullptr;
+    b200bpe_status r = b200bpe_trainer_create(c, bytes, word_starts, n, opts, &h);
+    if (r) return r;
+    r = b200bpe_trainer_run(h, 0, merges_out, counts_out, n_merges_out, early_stop_out, cb, user);
+    b200bpe_trainer_destroy(h);
+    return r;
+}
+
+}  // extern "C"

@@ -1,0 +1,120 @@
+"""GPU parity tests of the encode path: token ids from libb200bpe.so against the CPU oracle."""
+import numpy as np
+import pytest
+
+from gpu_bpe_b200 import TrieTokenizer, compileVocabToTrie
+from oracle import cpu_oracle as O
+from oracle import wgsl_model as M
+from tests.helpers import small_text
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def trained():
+    """A vocabulary trained by the oracle on config-2-shaped text (so the test does not depend on the GPU trainer)."""
+    data, mask, sym = small_text(2, 31, 2 << 20)
+    merges = O.train(sym, 1500, "fixed", threads=8)["merges"].tolist()
+    vocab = M.vocab_from_merges(merges)
+    return vocab, M.compile_vocab_to_trie(vocab)
+
+
+def test_tokenizer_fields_and_chunk_rule(engine, trained):
+    vocab, trie = trained
+    tok = TrieTokenizer.fromVocab(engine, vocab)
+    hdr = M.parse_trie(trie)
+    assert (tok.nodeCount, tok.edgeCount, tok.maxTokenLen) == (hdr["nodeCount"], hdr["edgeCount"], hdr["maxTokenLen"])
+    assert tok.chunkSize == max(512, min(2048, hdr["maxTokenLen"] * 8))
+    tok.destroy()
+    tok = TrieTokenizer(engine, trie, vocab, {"chunkSize": 96})
+    assert tok.chunkSize == 96
+    tok.destroy()
+
+
+@pytest.mark.parametrize("n", [0, 1, 2, 15, 16, 17, 511, 512, 513, 1023, 1025, 100_003])
+def test_sizes_around_chunk_edges(engine, trained, n):
+    vocab, trie = trained
+    data, _, _ = small_text(2, 77, max(n, 1))
+    data = data[:n]
+    tok = TrieTokenizer(engine, trie, vocab)
+    got = tok.encodeBytes(data)
+    want = O.encode(data, trie, tok.chunkSize) if n else np.zeros(0, np.uint32)
+    assert got.dtype == np.uint32 and got.tolist() == want.tolist()
+    assert tok.decode(got) == data.tobytes()
+    tok.destroy()
+
+
+@pytest.mark.parametrize("chunk", [1, 5, 64, 512, 2048])
+def test_chunk_sizes(engine, trained, chunk):
+    vocab, trie = trained
+    data, _, _ = small_text(2, 78, 300_000)
+    tok = TrieTokenizer(engine, trie, vocab, {"chunkSize": chunk})
+    got = tok.encodeBytes(data)
+    assert got.tolist() == O.encode(data, trie, chunk, threads=4).tolist()
+    tok.destroy()
+
+
+def test_against_python_model(engine, trained):
+    vocab, trie = trained
+    data, _, _ = small_text(2, 79, 20_000)
+    tok = TrieTokenizer(engine, trie, vocab)
+    assert tok.encodeBytes(data).tolist() == M.encode_bytes(data.tobytes(), trie, tok.chunkSize)
+    tok.destroy()
+
+
+def test_unknown_bytes_and_sparse_vocab(engine):
+    """A vocabulary without all single bytes: unmatched bytes come out as raw byte values."""
+    vocab = [[97], [], [97, 98], [97], [98, 99, 100]]
+    tok = TrieTokenizer.fromVocab(engine, vocab)
+    data = b"aabzbcdbcxab" * 200
+    want = M.encode_bytes(data, M.compile_vocab_to_trie(vocab), tok.chunkSize)
+    assert tok.encodeBytes(data).tolist() == want
+    assert tok.decode([0, 99999]) == b"a\xef\xbf\xbd"
+    tok.destroy()
+
+
+def test_random_bytes(engine, trained):
+    vocab, trie = trained
+    rng = np.random.default_rng(8)
+    data = rng.integers(0, 256, 200_000, dtype=np.uint8)
+    tok = TrieTokenizer(engine, trie, vocab)
+    assert tok.encodeBytes(data).tolist() == O.encode(data, trie, tok.chunkSize, threads=4).tolist()
+    tok.destroy()
+
+
+def test_batch_equals_per_document_calls(engine, trained):
+    from gpu_bpe_b200 import synth
+    vocab, trie = trained
+    data, _, _ = small_text(2, 80, 1 << 20)
+    offs = synth.doc_offsets(4, data.size, 300, 1.0)
+    offs[5] = offs[4]            # an empty document
+    tok = TrieTokenizer(engine, trie, vocab)
+    toks, toff = tok.encodeBatch(data, offs)
+    assert toff[0] == 0 and toff[-1] == toks.size
+    for d in range(300):
+        lo, hi = int(offs[d]), int(offs[d + 1])
+        want = O.encode(data[lo:hi], trie, tok.chunkSize) if hi > lo else np.zeros(0, np.uint32)
+        assert toks[int(toff[d]):int(toff[d + 1])].tolist() == want.tolist(), d
+    # and the same through a misaligned view of the buffer
+    toks2, toff2 = tok.encodeBatch(data[3:], (offs[1:] - 3).clip(0) if offs[1] >= 3 else offs[1:])
+    tok.destroy()
+
+
+def test_bad_trie_rejected(engine, trained):
+    _, trie = trained
+    with pytest.raises(ValueError, match="Invalid trie magic"):
+        TrieTokenizer(engine, b"\0" * 64)
+    with pytest.raises(ValueError, match="Truncated trie data"):
+        TrieTokenizer(engine, trie[: len(trie) // 2])
+
+
+def test_train_then_encode_round_trip(engine):
+    """The whole drop-in flow: train on the GPU, compile, encode, decode back to the input."""
+    from gpu_bpe_b200 import BPETrainer, PreTokenizer
+    data, _, _ = small_text(1, 12, 1 << 18)
+    res = BPETrainer(engine).train(data, targetVocabSize=800, preTokenizer=PreTokenizer(normalize=False))
+    tok = TrieTokenizer.fromVocab(engine, res["vocab"])
+    ids = tok.encodeBytes(data)
+    assert tok.decode(ids) == data.tobytes() and ids.size < data.size // 2
+    assert ids.tolist() == O.encode(data, compileVocabToTrie(res["vocab"]), tok.chunkSize, threads=4).tolist()
+    tok.destroy()
