@@ -3,6 +3,8 @@
 // the C entry points declared in include/b200bpe.h.
 #include <algorithm>
 #include <chrono>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -133,6 +135,8 @@ b200bpe_status Trainer::init_state() {
     // untouched tail is observable.
     B2_CUDA(cudaMemsetAsync(buf[1], 0, cap_elems * 4, s));
     B2_CUDA(cudaMemsetAsync(table, 0, sizeof(PairSlot) << table_log2, s));
+    // The look-back descriptors are tagged with the merge number, which restarts here.
+    B2_CUDA(cudaMemsetAsync(d_desc, 0, sizeof(unsigned long long) * ((n0 + MC_TILE - 1) / MC_TILE + 1), s));
     std::memset(h_state, 0, sizeof(DevState));
     h_state->n[0] = (uint32_t)n0;
     h_state->next_id = opts.first_token_id;
@@ -165,9 +169,17 @@ b200bpe_status Trainer::enqueue_merge(int iter, bool timed) {
     auto ev = [&](int k) -> cudaError_t {
         return timed ? cudaEventRecord(kev[(size_t)iter * 8 + k], s) : cudaSuccess;
     };
+    static const bool dbg = getenv("B200BPE_DEBUG_SYNC") != nullptr;
+    auto dsync = [&](const char* what) {
+        if (!dbg) return;
+        cudaError_t e = cudaStreamSynchronize(s);
+        fprintf(stderr, "[b200bpe] iter %d after %s: %s\n", iter, what, cudaGetErrorString(e));
+        fflush(stderr);
+    };
     B2_CUDA(ev(0));
     k_pair_count<PC_SLOTS_LOG2, PC_THREADS><<<grid_pc, PC_THREADS, (1 << PC_SLOTS_LOG2) * 12, s>>>(d_state, buf[0], buf[1], table);
     B2_CUDA(ev(1));
+    dsync("pair_count");
     if (ctx->world > 1) {
         b200bpe_status r = xch.enqueue(ctx, d_state, table, table_log2, d_cta_best, d_log, grid_am);
         if (r) return r;
@@ -177,9 +189,11 @@ b200bpe_status Trainer::enqueue_merge(int iter, bool timed) {
         k_argmax_setup<<<grid_am, AM_THREADS, 0, s>>>(d_state, table, d_cta_best, d_log, 0);
     }
     B2_CUDA(ev(3));
+    dsync("argmax_setup");
     if (literal) k_merge_compact<true><<<grid_mc, MC_THREADS, 0, s>>>(d_state, buf[0], buf[1], d_desc);
     else k_merge_compact<false><<<grid_mc, MC_THREADS, 0, s>>>(d_state, buf[0], buf[1], d_desc);
     B2_CUDA(ev(4));
+    dsync("merge_compact");
     B2_CUDA(cudaGetLastError());
     return B200BPE_OK;
 }
@@ -280,6 +294,10 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
             const size_t o = (size_t)(before + i - start_done);
             if (merges_out) { merges_out[o * 3 + 0] = l[0]; merges_out[o * 3 + 1] = l[1]; merges_out[o * 3 + 2] = l[2]; }
             if (counts_out) counts_out[o] = l[3];
+        }
+        if (got == 0 && !h_state->early_stop && h_state->status == DS_OK && !h_state->want_grow) {
+            set_last_error("a batch made no progress");
+            return B200BPE_ERR_INTERNAL;
         }
         merges_done = done_now;
         remaining -= got;

@@ -73,14 +73,17 @@ k_pair_count(DevState* __restrict__ st, const uint32_t* __restrict__ buf0, const
     unsigned long long* skey = reinterpret_cast<unsigned long long*>(pc_smem);
     uint32_t* scnt = reinterpret_cast<uint32_t*>(skey + S);
 
-    if (st->early_stop | st->target_hit | st->status) return;
+    // One thread reads the stop flags for the whole CTA: `status` can change while this kernel
+    // runs (another CTA may find the table full), and a CTA must not split at a barrier.
+    __shared__ uint32_t s_idle;
+    if (threadIdx.x == 0) s_idle = st->early_stop | st->target_hit | st->status;
+    for (int i = threadIdx.x; i < S; i += THREADS) { skey[i] = 0ull; scnt[i] = 0u; }
+    __syncthreads();
+    if (s_idle) return;
     const uint32_t e = st->epoch;
     const uint32_t N = st->n[e & 1];
     const uint32_t* __restrict__ src = (e & 1) ? buf1 : buf0;
     const uint32_t logC = st->table_log2;
-
-    for (int i = threadIdx.x; i < S; i += THREADS) { skey[i] = 0ull; scnt[i] = 0u; }
-    __syncthreads();
 
     const uint32_t nvec = (N + 3u) >> 2;
     uint32_t per = (nvec + gridDim.x - 1) / gridDim.x;
@@ -145,10 +148,6 @@ k_pair_count(DevState* __restrict__ st, const uint32_t* __restrict__ buf0, const
 }
 
 // ─────────────────────────────── arg-max + clear + set-up ───────────────────────────────
-struct SetupOut {
-    uint32_t* log;  // 4 words per merge: a, b, new_id, count
-};
-
 __device__ __forceinline__ void warp_best(uint32_t& c, unsigned long long& k) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -181,7 +180,7 @@ __device__ __forceinline__ void setup_merge(DevState* st, uint32_t best_count, u
 
 // mode 0: single GPU — finish with setup_merge.
 // mode 1: sharded — the last CTA only publishes this rank's best as a packed word for the
-//         all-reduce (count << 32 | ~pair32); k_setup_from_packed finishes after the collective.
+//         all-reduce (count << 32 | ~pair32); k_unpack_flags finishes after the collective.
 __global__ void __launch_bounds__(AM_THREADS)
 k_argmax_setup(DevState* __restrict__ st, PairSlot* __restrict__ table, CtaBest* __restrict__ cta_best,
                uint32_t* __restrict__ log, int mode) {
@@ -189,7 +188,12 @@ k_argmax_setup(DevState* __restrict__ st, PairSlot* __restrict__ table, CtaBest*
     __shared__ unsigned long long sk[AM_THREADS / 32];
     __shared__ uint32_t socc[AM_THREADS / 32];
     __shared__ bool is_last;
-    if (st->early_stop | st->target_hit) return;
+    // Neither flag changes before every CTA has passed this test: only the last CTA to finish
+    // writes them.  Once the run has stopped, nothing is left for the merge kernel to apply.
+    if (st->early_stop | st->target_hit) {
+        if (blockIdx.x == 0 && threadIdx.x == 0) st->active = 0u;
+        return;
+    }
     const uint32_t C = 1u << st->table_log2;
     uint4* __restrict__ t4 = reinterpret_cast<uint4*>(table);
     uint32_t bc = 0, occ = 0;
@@ -258,19 +262,6 @@ k_argmax_setup(DevState* __restrict__ st, PairSlot* __restrict__ table, CtaBest*
     }
 }
 
-// Sharded runs: every rank decodes the same all-reduced (count, pair) word and sets up the merge.
-__global__ void k_setup_from_packed(DevState* __restrict__ st, const unsigned long long* __restrict__ packed_max,
-                                    const uint32_t* __restrict__ status_max, uint32_t* __restrict__ log) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
-    if (st->early_stop | st->target_hit) return;
-    if (*status_max != DS_OK && st->status == DS_OK) st->status = *status_max;
-    const unsigned long long p = *packed_max;
-    const uint32_t cnt = (uint32_t)(p >> 32);
-    const uint32_t pair32 = ~(uint32_t)p;
-    const unsigned long long key = ((unsigned long long)(pair32 >> 16) << 32) | (pair32 & 0xFFFFu);
-    setup_merge(st, cnt, cnt ? key : 0ull, log);
-}
-
 // ─────────────────────────────── merge + scan + compaction ───────────────────────────────
 // Tile descriptor of the decoupled look-back: high word = (tag << 2) | flag, low word = value.
 // The tag is the merge number + 1, so descriptors left by earlier merges read as "not ready"
@@ -291,6 +282,8 @@ __global__ void __launch_bounds__(MC_THREADS)
 k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsigned long long* __restrict__ desc) {
     __shared__ uint32_t wsum[MC_ROWS * (MC_THREADS / 32)];
     __shared__ uint32_t s_tile, s_base;
+    // `active`, `k3_epoch`, `n[k3_epoch & 1]`, `a`, `b`, `new_id` and `max_count` are written by the
+    // set-up step only, so every thread of every CTA of this launch reads the same values.
     if (!st->active) return;
     const uint32_t e = st->k3_epoch;
     const uint32_t N = st->n[e & 1];
@@ -429,7 +422,6 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                         atomicExch(&st->status, (uint32_t)DS_INTERNAL);
                     st->n[(e + 1u) & 1u] = LITERAL ? nnew : total;
                     st->epoch = e + 1u;
-                    st->active = 0u;
                 }
             }
         }
