@@ -68,6 +68,7 @@ SIGNATURES = {
     "b200bpe_trainer_pair_counts": (C.c_int32, [C.c_void_p, u64p, u32p, C.c_uint64, u64p]),
     "b200bpe_trainer_kernel_stats": (C.c_int32, [C.c_void_p, C.POINTER(KernelStats)]),
     "b200bpe_trainer_last_run_ms": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double)]),
+    "b200bpe_trainer_last_reset_ms": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double)]),
     "b200bpe_trainer_destroy": (None, [C.c_void_p]),
     "b200bpe_trie_compile": (C.c_int32, [C.c_void_p, u64p, C.c_uint32, C.c_void_p, C.POINTER(C.c_size_t)]),
     "b200bpe_trie_parse_header": (C.c_int32, [C.c_void_p, C.c_size_t, u32p]),

@@ -58,7 +58,7 @@ struct Trainer {
     uint64_t cur_n = 0;
     // timing
     cudaEvent_t ev_run0 = nullptr, ev_run1 = nullptr;
-    double last_run_ms = 0;
+    double last_run_ms = 0, last_reset_ms = 0;
     std::vector<cudaEvent_t> kev;
     b200bpe_kernel_stats stats{};
 
@@ -102,7 +102,7 @@ b200bpe_status Trainer::alloc_common() {
     B2_CUDA(cudaMallocHost(&h_log, log_bytes));
     const int sms = ctx->sm_count;
     const uint64_t nvec = (n0 + 3) / 4;
-    grid_pc = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)sms * 2, (nvec + PC_THREADS - 1) / PC_THREADS));
+    grid_pc = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)sms * PC_CTAS_PER_SM, (nvec + PC_THREADS - 1) / PC_THREADS));
     grid_am = std::max(1, std::min(sms * 4, (int)((1u << table_log2) / (AM_THREADS * 4))));
     const uint64_t ntiles = (n0 + MC_TILE - 1) / MC_TILE;
     grid_mc = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)sms * 8, ntiles));
@@ -111,8 +111,8 @@ b200bpe_status Trainer::alloc_common() {
     B2_CUDA(cudaMemsetAsync(d_desc, 0, sizeof(unsigned long long) * (ntiles + 1), ctx->stream));
     B2_CUDA(cudaEventCreate(&ev_run0));
     B2_CUDA(cudaEventCreate(&ev_run1));
-    B2_CUDA(cudaFuncSetAttribute(k_pair_count<PC_SLOTS_LOG2, PC_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (1 << PC_SLOTS_LOG2) * 12));
+    B2_CUDA(cudaFuncSetAttribute(k_pair_count<PC_SLOTS, PC_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PC_SMEM_BYTES));
     if (ctx->world > 1) {
         b200bpe_status s = xch.init(ctx, table_log2);
         if (s) return s;
@@ -124,6 +124,7 @@ b200bpe_status Trainer::alloc_common() {
 // state of a fresh BPETrainer.train call (trainer.js:187-196).
 b200bpe_status Trainer::init_state() {
     cudaStream_t s = ctx->stream;
+    B2_CUDA(cudaEventRecord(ev_run0, s));
     if (d_sym_init) {
         B2_CUDA(cudaMemcpyAsync(buf[0], d_sym_init, n0 * 4, cudaMemcpyDeviceToDevice, s));
     } else {
@@ -144,7 +145,13 @@ b200bpe_status Trainer::init_state() {
     h_state->literal = (opts.compat_mode == B200BPE_COMPAT_LITERAL) ? 1u : 0u;
     h_state->world = (uint32_t)ctx->world;
     B2_CUDA(cudaMemcpyAsync(d_state, h_state, sizeof(DevState), cudaMemcpyHostToDevice, s));
+    B2_CUDA(cudaEventRecord(ev_run1, s));
     B2_CUDA(cudaStreamSynchronize(s));
+    {
+        float ms = 0;
+        cudaEventElapsedTime(&ms, ev_run0, ev_run1);
+        last_reset_ms = ms;
+    }
     merges_done = 0;
     early_stop = false;
     cur_n = n0;
@@ -177,7 +184,7 @@ b200bpe_status Trainer::enqueue_merge(int iter, bool timed) {
         fflush(stderr);
     };
     B2_CUDA(ev(0));
-    k_pair_count<PC_SLOTS_LOG2, PC_THREADS><<<grid_pc, PC_THREADS, (1 << PC_SLOTS_LOG2) * 12, s>>>(d_state, buf[0], buf[1], table);
+    k_pair_count<PC_SLOTS, PC_THREADS><<<grid_pc, PC_THREADS, PC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], table);
     B2_CUDA(ev(1));
     dsync("pair_count");
     if (ctx->world > 1) {
@@ -465,7 +472,7 @@ b200bpe_status b200bpe_trainer_pair_counts(b200bpe_trainer* h, uint64_t* keys_ou
     cudaStream_t s = t->ctx->stream;
     for (int attempt = 0; attempt < 12; attempt++) {
         k_begin_batch<<<1, 1, 0, s>>>(t->d_state, 0xFFFFFFFFu);
-        k_pair_count<PC_SLOTS_LOG2, PC_THREADS><<<t->grid_pc, PC_THREADS, (1 << PC_SLOTS_LOG2) * 12, s>>>(
+        k_pair_count<PC_SLOTS, PC_THREADS><<<t->grid_pc, PC_THREADS, PC_SMEM_BYTES, s>>>(
             t->d_state, t->buf[0], t->buf[1], t->table);
         PairSlot* tab = t->table;
         uint32_t tl2 = t->table_log2;
@@ -514,6 +521,12 @@ b200bpe_status b200bpe_trainer_kernel_stats(b200bpe_trainer* h, b200bpe_kernel_s
 b200bpe_status b200bpe_trainer_last_run_ms(b200bpe_trainer* h, double* ms) {
     if (!h || !ms) return B200BPE_ERR_BAD_ARG;
     *ms = h->t->last_run_ms;
+    return B200BPE_OK;
+}
+
+b200bpe_status b200bpe_trainer_last_reset_ms(b200bpe_trainer* h, double* ms) {
+    if (!h || !ms) return B200BPE_ERR_BAD_ARG;
+    *ms = h->t->last_reset_ms;
     return B200BPE_OK;
 }
 

@@ -18,13 +18,16 @@
 namespace b200bpe {
 
 constexpr int PC_THREADS = 1024;     // pair count: threads per CTA
-constexpr int PC_SLOTS_LOG2 = 13;    // pair count: shared-memory table slots per CTA (8192 * 12 B = 96 KB)
-constexpr int PC_LOCAL_PROBES = 4;   // linear probes in shared memory before going to the global table
+constexpr int PC_SLOTS = 12288;      // pair count: shared-memory slots per CTA (8 B each = 96 KB: two CTAs per SM)
+constexpr int PC_CTAS_PER_SM = 2;
+constexpr int PC_SMEM_BYTES = PC_SLOTS * 8;
+constexpr int PC_LOCAL_PROBES = 2;   // linear probes in shared memory before going to the global table
 constexpr int TABLE_MAX_PROBE = 1024;
 constexpr int AM_THREADS = 256;
 constexpr int MC_THREADS = 256;
 constexpr int MC_ROWS = 4;                               // uint4 rows per thread
 constexpr int MC_TILE = MC_THREADS * 4 * MC_ROWS;        // 4096 symbols per tile
+constexpr int MC_WARPS = MC_THREADS / 32;
 constexpr uint32_t LOOKBACK_MAX_SPINS = 1u << 22;        // bounded wait; then DS_LOOKBACK_TIMEOUT
 
 __device__ __forceinline__ uint32_t hash_pair(unsigned long long key) {
@@ -60,24 +63,48 @@ __device__ __forceinline__ void table_add(PairSlot* __restrict__ table, uint32_t
 }
 
 // ─────────────────────────────── pair count ───────────────────────────────
-// Each CTA owns one contiguous span of the symbol array, reads it with 16-byte loads, and
-// aggregates pairs in a shared-memory table; whatever does not fit there after a few probes
-// goes straight to the global table with one atomic per distinct key per warp.  At the end the
-// shared table is flushed, one global add per occupied slot.
-template <int S_LOG2, int THREADS>
-__global__ void __launch_bounds__(THREADS)
+// Each CTA owns one contiguous span of the symbol array and reads it with 16-byte loads.
+// Pairs are first aggregated in a shared-memory table: 32-bit keys (left << 16 | right) and
+// 32-bit counts in two arrays, so a hit costs one 32-bit shared load and one native 32-bit shared
+// atomic add.  A pair that finds no room within a few probes goes straight to the global table,
+// one atomic per distinct key per warp (match-any aggregation).  At the end the shared table is
+// flushed into the global table of 64-bit (left << 32 | right) keys, one add per occupied slot.
+__device__ __forceinline__ uint32_t smem_slot(uint32_t key32, uint32_t nslots) {
+    return __umulhi(key32 * 0x9E3779B1u, nslots);
+}
+
+__device__ __forceinline__ bool smem_count(uint32_t* __restrict__ skey, uint32_t* __restrict__ scnt, uint32_t nslots,
+                                           uint32_t key32) {
+    uint32_t slot = smem_slot(key32, nslots);
+#pragma unroll
+    for (int p = 0; p < PC_LOCAL_PROBES; p++) {
+        uint32_t cur = skey[slot];
+        if (cur == 0u) {
+            cur = atomicCAS(&skey[slot], 0u, key32);
+            if (cur == 0u) cur = key32;
+        }
+        if (cur == key32) {
+            atomicAdd(&scnt[slot], 1u);
+            return true;
+        }
+        slot = slot + 1 == nslots ? 0u : slot + 1;
+    }
+    return false;
+}
+
+template <int S, int THREADS>
+__global__ void __launch_bounds__(THREADS, PC_CTAS_PER_SM)
 k_pair_count(DevState* __restrict__ st, const uint32_t* __restrict__ buf0, const uint32_t* __restrict__ buf1,
              PairSlot* __restrict__ table) {
-    constexpr int S = 1 << S_LOG2;
     extern __shared__ __align__(16) unsigned char pc_smem[];
-    unsigned long long* skey = reinterpret_cast<unsigned long long*>(pc_smem);
-    uint32_t* scnt = reinterpret_cast<uint32_t*>(skey + S);
+    uint32_t* skey = reinterpret_cast<uint32_t*>(pc_smem);
+    uint32_t* scnt = skey + S;
 
     // One thread reads the stop flags for the whole CTA: `status` can change while this kernel
     // runs (another CTA may find the table full), and a CTA must not split at a barrier.
     __shared__ uint32_t s_idle;
     if (threadIdx.x == 0) s_idle = st->early_stop | st->target_hit | st->status;
-    for (int i = threadIdx.x; i < S; i += THREADS) { skey[i] = 0ull; scnt[i] = 0u; }
+    for (int i = threadIdx.x; i < 2 * S; i += THREADS) skey[i] = 0u;
     __syncthreads();
     if (s_idle) return;
     const uint32_t e = st->epoch;
@@ -105,44 +132,51 @@ k_pair_count(DevState* __restrict__ st, const uint32_t* __restrict__ buf0, const
         }
         const uint32_t rem = in ? (N - 4u * v) : 0u;  // symbols of this vector that are live
         const uint32_t s[5] = {q.x, q.y, q.z, q.w, nx};
+        uint32_t pend_mask = 0u;
+        uint32_t keys[4];
+        // Fast path, the same instructions for every lane: probe the home slot; a lane whose pair is
+        // already there adds 1 with one predicated atomic.
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            const uint32_t a = s[j] & TOKEN_MASK, rb = s[j + 1], b = rb & TOKEN_MASK;
-            const bool ok = ((uint32_t)(j + 1) < rem) && !(rb & WORD_START_BIT) && a != 0u && b != 0u;
-            const unsigned long long key = ((unsigned long long)a << 32) | b;
-            const uint32_t h = hash_pair(key);
-            bool pending = ok;
-            if (ok) {
-                uint32_t slot = h & (S - 1);
+            // key32 = (left token << 16) | right token; a pair needs a live right neighbour that
+            // does not start a word, and neither token may be 0 (train.wgsl:393-398)
+            keys[j] = __byte_perm(s[j + 1], s[j], 0x5410);
+            const bool ok = ((uint32_t)(j + 1) < rem) && !(s[j + 1] & WORD_START_BIT) && (keys[j] & 0xFFFFu) != 0u &&
+                            (keys[j] >> 16) != 0u;
+            const uint32_t slot = smem_slot(keys[j], S);
+            const bool hit = ok && skey[slot] == keys[j];
+            if (hit) atomicAdd(&scnt[slot], 1u);
+            if (ok && !hit) pend_mask |= 1u << j;
+        }
+        // Slow path, only when some lane missed: insert with compare-and-swap, probe further.
+        if (__any_sync(0xFFFFFFFFu, pend_mask != 0u)) {
 #pragma unroll
-                for (int p = 0; p < PC_LOCAL_PROBES; p++) {
-                    unsigned long long k = skey[slot];
-                    if (k == 0ull) {
-                        k = atomicCAS(&skey[slot], 0ull, key);
-                        if (k == 0ull) k = key;
+            for (int j = 0; j < 4; j++)
+                if (((pend_mask >> j) & 1u) && smem_count(skey, scnt, S, keys[j])) pend_mask &= ~(1u << j);
+        }
+        // Overflow (rare while the shared table has room): one global add per distinct key among
+        // the pending lanes of this warp.
+        if (__any_sync(0xFFFFFFFFu, pend_mask != 0u)) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const bool pending = (pend_mask >> j) & 1u;
+                const uint32_t pend = __ballot_sync(0xFFFFFFFFu, pending);
+                if (pending) {
+                    const uint32_t peers = __match_any_sync(pend, keys[j]);
+                    if (lane == __ffs(peers) - 1) {
+                        const unsigned long long key = ((unsigned long long)(keys[j] >> 16) << 32) | (keys[j] & 0xFFFFu);
+                        table_add(table, logC, key, hash_pair(key), __popc(peers), st);
                     }
-                    if (k == key) {
-                        atomicAdd(&scnt[slot], 1u);
-                        pending = false;
-                        break;
-                    }
-                    slot = (slot + 1) & (S - 1);
                 }
-            }
-            // Overflow: one global add per distinct key among the pending lanes of this warp.
-            const uint32_t pend = __ballot_sync(0xFFFFFFFFu, pending);
-            if (pending) {
-                const uint32_t peers = __match_any_sync(pend, key);
-                if (lane == __ffs(peers) - 1) table_add(table, logC, key, h, __popc(peers), st);
             }
         }
     }
     __syncthreads();
     for (int i = threadIdx.x; i < S; i += THREADS) {
-        const uint32_t c = scnt[i];
-        if (c) {
-            const unsigned long long key = skey[i];
-            table_add(table, logC, key, hash_pair(key), c, st);
+        const uint32_t k32 = skey[i];
+        if (k32 != 0u) {
+            const unsigned long long key = ((unsigned long long)(k32 >> 16) << 32) | (k32 & 0xFFFFu);
+            table_add(table, logC, key, hash_pair(key), scnt[i], st);
         }
     }
 }
@@ -265,7 +299,7 @@ k_argmax_setup(DevState* __restrict__ st, PairSlot* __restrict__ table, CtaBest*
 // ─────────────────────────────── merge + scan + compaction ───────────────────────────────
 // Tile descriptor of the decoupled look-back: high word = (tag << 2) | flag, low word = value.
 // The tag is the merge number + 1, so descriptors left by earlier merges read as "not ready"
-// and the array never needs clearing.
+// and the array never needs clearing between merges.
 constexpr uint32_t DESC_AGG = 1u, DESC_PREFIX = 2u;
 
 __device__ __forceinline__ unsigned long long ld_desc(const unsigned long long* p) {
@@ -277,11 +311,51 @@ __device__ __forceinline__ void st_desc(unsigned long long* p, unsigned long lon
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
+// Exclusive offset of `tile` = sum of the kept counts of all earlier tiles (one warp).
+// Bounded wait: if a predecessor never shows up, *timed_out is set and 0 is returned.
+__device__ __forceinline__ uint32_t lookback(const unsigned long long* __restrict__ desc, uint32_t tile, uint32_t tag,
+                                             int lane, bool* timed_out) {
+    uint32_t excl = 0u, spins = 0u;
+    int pos = (int)tile - 1;
+    for (;;) {
+        const int idx = pos - lane;
+        uint32_t hi = (tag << 2) | DESC_PREFIX;  // positions before tile 0 act as a zero prefix
+        uint32_t val = 0u;
+        for (;;) {
+            if (idx >= 0) {
+                const unsigned long long d = ld_desc(desc + idx);
+                hi = (uint32_t)(d >> 32);
+                val = (uint32_t)d;
+            }
+            const bool ready = ((hi >> 2) == tag) && (hi & 3u) != 0u;
+            if (__all_sync(0xFFFFFFFFu, ready)) break;
+            if (++spins > LOOKBACK_MAX_SPINS) { *timed_out = true; return 0u; }
+            __nanosleep(20);
+        }
+        const uint32_t pmask = __ballot_sync(0xFFFFFFFFu, (hi & 3u) == DESC_PREFIX);
+        const int first = pmask ? (__ffs(pmask) - 1) : 32;  // nearest predecessor holding a full prefix
+        uint32_t contrib = (lane <= first) ? val : 0u;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xFFFFFFFFu, contrib, o);
+        excl += contrib;
+        if (pmask) return excl;
+        pos -= 32;
+    }
+}
+
+// One tile = 4096 symbols; warp w owns the 512 consecutive symbols [w * 512, (w + 1) * 512) of the
+// tile as four 16-byte rows per lane, so a warp's kept symbols are contiguous in the output.
+// Per tile: load, decide per symbol (rewritten? dropped?), rank within the warp, publish the
+// tile's kept count, stage the kept symbols in shared memory at their tile-local rank while
+// warp 0 looks back for the tile's global offset, then copy the staged run out with coalesced
+// stores.  Tiles are handed out by an atomic ticket so that a waiting tile's predecessors are
+// always running.
 template <bool LITERAL>
-__global__ void __launch_bounds__(MC_THREADS)
+__global__ void __launch_bounds__(MC_THREADS, 6)
 k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsigned long long* __restrict__ desc) {
-    __shared__ uint32_t wsum[MC_ROWS * (MC_THREADS / 32)];
-    __shared__ uint32_t s_tile, s_base;
+    __shared__ uint32_t stage[MC_TILE];
+    __shared__ uint32_t wsum[MC_WARPS];
+    __shared__ uint32_t s_tile, s_base, s_agg;
     // `active`, `k3_epoch`, `n[k3_epoch & 1]`, `a`, `b`, `new_id` and `max_count` are written by the
     // set-up step only, so every thread of every CTA of this launch reads the same values.
     if (!st->active) return;
@@ -296,124 +370,142 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint4* src4 = reinterpret_cast<const uint4*>(src);
 
+    if (threadIdx.x == 0) s_tile = atomicAdd(&st->ticket, 1u);
+    __syncthreads();
     for (;;) {
-        __syncthreads();
-        if (threadIdx.x == 0) s_tile = atomicAdd(&st->ticket, 1u);
-        __syncthreads();
         const uint32_t tile = s_tile;
         if (tile >= ntiles) break;
-        const uint32_t vbase = tile * (MC_TILE / 4);
+        const uint32_t vwarp = tile * (MC_TILE / 4) + warp * (MC_ROWS * 32);  // first vector of this warp
 
         uint4 q[MC_ROWS];
-        uint32_t pv[MC_ROWS], nx[MC_ROWS];
 #pragma unroll
         for (int j = 0; j < MC_ROWS; j++) {
-            const uint32_t v = vbase + j * MC_THREADS + threadIdx.x;
-            const uint32_t i = 4u * v;
-            q[j] = (i < N) ? src4[v] : make_uint4(0u, 0u, 0u, 0u);
+            const uint32_t v = vwarp + j * 32 + lane;
+            q[j] = (4u * v < N) ? src4[v] : make_uint4(0u, 0u, 0u, 0u);
         }
+        // the symbols just outside the warp's span come from global memory
+        uint32_t edge_prev = 0u, edge_next = 0u;
+        {
+            const uint32_t i0 = 4u * vwarp, i1 = 4u * (vwarp + MC_ROWS * 32);
+            if (lane == 0) edge_prev = (i0 > 0u && i0 - 1u < N) ? src[i0 - 1u] : 0u;
+            if (lane == 31) edge_next = (i1 < N) ? src[i1] : 0u;
+        }
+        // row-crossing neighbours: lane 0 needs the previous row's lane 31, lane 31 the next row's lane 0
+        uint32_t first_x[MC_ROWS], last_w[MC_ROWS];
 #pragma unroll
         for (int j = 0; j < MC_ROWS; j++) {
-            const uint32_t v = vbase + j * MC_THREADS + threadIdx.x;
-            const uint32_t i = 4u * v;
-            pv[j] = __shfl_up_sync(0xFFFFFFFFu, q[j].w, 1);
-            nx[j] = __shfl_down_sync(0xFFFFFFFFu, q[j].x, 1);
-            if (lane == 0) pv[j] = (i > 0u && i - 1u < N) ? src[i - 1u] : 0u;
-            if (lane == 31) nx[j] = (i + 4u < N) ? src[i + 4u] : 0u;
+            first_x[j] = __shfl_sync(0xFFFFFFFFu, q[j].x, 0);
+            last_w[j] = __shfl_sync(0xFFFFFFFFu, q[j].w, 31);
+        }
+        uint32_t keep = 0u;        // 4 bits per row
+        uint32_t rank[MC_ROWS];    // tile-local rank of this lane's first kept symbol of row j, within the warp
+        uint32_t run = 0u;         // kept symbols of the warp's earlier rows
+        // A warp whose whole span (and the symbol after it) lies below both N and the compaction
+        // limit needs no bounds tests.
+        const bool interior = 4u * (vwarp + MC_ROWS * 32) < min(N, limit);
+#pragma unroll
+        for (int j = 0; j < MC_ROWS; j++) {
+            uint32_t pv = __shfl_up_sync(0xFFFFFFFFu, q[j].w, 1);
+            uint32_t nx = __shfl_down_sync(0xFFFFFFFFu, q[j].x, 1);
+            if (lane == 0) pv = j > 0 ? last_w[j > 0 ? j - 1 : 0] : edge_prev;
+            if (lane == 31) nx = j < MC_ROWS - 1 ? first_x[j < MC_ROWS - 1 ? j + 1 : j] : edge_next;
             if (LITERAL) {
                 // A neighbour owned by another thread may already carry this merge's in-place
                 // rewrite; the new id is fresh, so mapping it back to `a` restores the snapshot.
-                if ((pv[j] & TOKEN_MASK) == NW) pv[j] = (pv[j] & WORD_START_BIT) | A;
-                if ((nx[j] & TOKEN_MASK) == NW) nx[j] = (nx[j] & WORD_START_BIT) | A;
+                if ((pv & TOKEN_MASK) == NW) pv = (pv & WORD_START_BIT) | A;
+                if ((nx & TOKEN_MASK) == NW) nx = (nx & WORD_START_BIT) | A;
             }
-        }
-
-        uint32_t outv[MC_ROWS][4];
-        uint32_t keep[MC_ROWS];  // 4 keep bits per row
-        uint32_t lane_excl[MC_ROWS];
+            const uint32_t s[6] = {pv, q[j].x, q[j].y, q[j].z, q[j].w, nx};
+            // left[k]: s[k] is `a`; right[k]: s[k] is `b` and does not start a word.  A pair matches at
+            // k when left[k] & right[k + 1]; the symbol at k + 1 is then dropped (train.wgsl:482-497).
+            uint32_t left = 0u, right = 0u;
 #pragma unroll
-        for (int j = 0; j < MC_ROWS; j++) {
-            const uint32_t i0 = 4u * (vbase + j * MC_THREADS + threadIdx.x);
-            const uint32_t s[6] = {pv[j], q[j].x, q[j].y, q[j].z, q[j].w, nx[j]};
-            uint32_t kb = 0u;
+            for (int k = 0; k < 6; k++) {
+                left |= ((s[k] & TOKEN_MASK) == A ? 1u : 0u) << k;
+                right |= ((s[k] & (TOKEN_MASK | WORD_START_BIT)) == B ? 1u : 0u) << k;
+            }
+            uint32_t match = left & (right >> 1);           // bit k: pair (k, k + 1) merges; k = 0 is the left neighbour
+            uint32_t kb;
+            if (interior) {
+                kb = ~match & 15u;                          // own symbol k (bit k + 1 of s) is dropped iff match bit k
+                match = (match >> 1) & 15u;                 // own symbol k is rewritten iff pair (k + 1, k + 2) of s matches
+            } else {
+                const uint32_t i0 = 4u * (vwarp + j * 32 + lane);
+                uint32_t live = 0u, pairable = 0u, below = 0u;
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    live |= (i0 + k < N ? 1u : 0u) << k;
+                    pairable |= (i0 + k + 1u < N ? 1u : 0u) << k;
+                    below |= (i0 + k < limit ? 1u : 0u) << k;
+                }
+                // a match needs both symbols live: own pairs by `pairable`, the left neighbour's pair by own bit 0
+                const uint32_t m_own = (match >> 1) & pairable;
+                const uint32_t m_prev = (match & 1u) & live;
+                kb = ~((m_own << 1) | m_prev) & live & below & 15u;
+                match = m_own;
+            }
+            uint32_t ov[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
 #pragma unroll
             for (int k = 0; k < 4; k++) {
-                const uint32_t i = i0 + k;
-                const uint32_t cur = s[k + 1], prv = s[k], nxt = s[k + 2];
-                const bool inr = i < N;
-                const bool match_a = inr && (i + 1u < N) && !(nxt & WORD_START_BIT) &&
-                                     (cur & TOKEN_MASK) == A && (nxt & TOKEN_MASK) == B;
-                const bool invalid = (i > 0u) && !(cur & WORD_START_BIT) && (prv & TOKEN_MASK) == A &&
-                                     (cur & TOKEN_MASK) == B;
-                const uint32_t ov = match_a ? (NW | (cur & WORD_START_BIT)) : cur;
-                outv[j][k] = ov;
-                if (inr && !invalid && i < limit) kb |= 1u << k;
-                if (LITERAL && match_a) src[i] = ov;  // the reference rewrites the source in place
+                if ((match >> k) & 1u) {
+                    ov[k] = NW | (ov[k] & WORD_START_BIT);
+                    if (LITERAL) src[4u * (vwarp + j * 32 + lane) + k] = ov[k];  // the reference rewrites the source in place
+                }
             }
-            keep[j] = kb;
-            uint32_t c = __popc(kb), incl = c;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-                if (lane >= o) incl += t;
-            }
-            lane_excl[j] = incl - c;
-            if (lane == 31) wsum[j * (MC_THREADS / 32) + warp] = incl;
-        }
-        __syncthreads();
-        if (warp == 0) {
-            // 32 warp-row totals in index order → exclusive offsets + tile aggregate
-            const uint32_t w = wsum[lane];
-            uint32_t incl = w;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-                if (lane >= o) incl += t;
-            }
-            wsum[lane] = incl - w;
-            const uint32_t agg = __shfl_sync(0xFFFFFFFFu, incl, 31);
-            uint32_t excl = 0u;
-            if (tile == 0u) {
-                if (lane == 0) st_desc(desc, ((unsigned long long)((tag << 2) | DESC_PREFIX) << 32) | agg);
+            q[j] = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+            keep |= kb << (4 * j);
+            const uint32_t c = __popc(kb);
+            if (__all_sync(0xFFFFFFFFu, c == 4u)) {
+                rank[j] = run + 4u * lane;                   // nothing dropped in this row: ranks are positions
+                run += 128u;
             } else {
-                if (lane == 0) st_desc(desc + tile, ((unsigned long long)((tag << 2) | DESC_AGG) << 32) | agg);
-                int pos = (int)tile - 1;
-                uint32_t spins = 0;
-                bool timed_out = false;
-                for (;;) {
-                    const int idx = pos - lane;
-                    unsigned long long d = 0ull;
-                    uint32_t hi = (tag << 2) | DESC_PREFIX;  // positions before tile 0 act as a zero prefix
-                    uint32_t val = 0u;
-                    for (;;) {
-                        if (idx >= 0) {
-                            d = ld_desc(desc + idx);
-                            hi = (uint32_t)(d >> 32);
-                            val = (uint32_t)d;
-                        }
-                        const bool ready = ((hi >> 2) == tag) && (hi & 3u) != 0u;
-                        if (__all_sync(0xFFFFFFFFu, ready)) break;
-                        if (++spins > LOOKBACK_MAX_SPINS) { timed_out = true; break; }
-                        __nanosleep(40);
-                    }
-                    if (timed_out) break;
-                    const uint32_t pmask = __ballot_sync(0xFFFFFFFFu, (hi & 3u) == DESC_PREFIX);
-                    const int first = pmask ? (__ffs(pmask) - 1) : 32;  // nearest predecessor holding a full prefix
-                    uint32_t contrib = (lane <= first) ? val : 0u;
+                uint32_t incl = c;
 #pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xFFFFFFFFu, contrib, o);
-                    excl += contrib;
-                    if (pmask) break;
-                    pos -= 32;
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                    if (lane >= o) incl += t;
                 }
-                if (timed_out) {
-                    if (lane == 0) atomicExch(&st->status, (uint32_t)DS_LOOKBACK_TIMEOUT);
-                    excl = 0u;
-                }
+                rank[j] = run + incl - c;
+                run += __shfl_sync(0xFFFFFFFFu, incl, 31);
+            }
+        }
+        if (lane == 0) wsum[warp] = run;
+        __syncthreads();  // (B) warp totals visible; nobody reads s_tile after this point
+
+        // tile-local offset of this warp and the tile aggregate
+        uint32_t w = lane < MC_WARPS ? wsum[lane] : 0u;
+        uint32_t before = lane < warp ? w : 0u;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            before += __shfl_xor_sync(0xFFFFFFFFu, before, o);
+            w += __shfl_xor_sync(0xFFFFFFFFu, w, o);
+        }
+        const uint32_t agg = w;
+        if (warp == 0 && lane == 0) {
+            const uint32_t flag = tile == 0u ? DESC_PREFIX : DESC_AGG;
+            st_desc(desc + tile, ((unsigned long long)((tag << 2) | flag) << 32) | agg);
+        }
+        // stage the kept symbols at their tile-local rank
+#pragma unroll
+        for (int j = 0; j < MC_ROWS; j++) {
+            uint32_t d = before + rank[j];
+            const uint32_t kb = (keep >> (4 * j)) & 15u;
+            if (kb & 1u) stage[d++] = q[j].x;
+            if (kb & 2u) stage[d++] = q[j].y;
+            if (kb & 4u) stage[d++] = q[j].z;
+            if (kb & 8u) stage[d++] = q[j].w;
+        }
+        if (warp == 0) {
+            uint32_t excl = 0u;
+            if (tile != 0u) {
+                bool timed_out = false;
+                excl = lookback(desc, tile, tag, lane, &timed_out);
+                if (timed_out && lane == 0) atomicExch(&st->status, (uint32_t)DS_LOOKBACK_TIMEOUT);
                 if (lane == 0) st_desc(desc + tile, ((unsigned long long)((tag << 2) | DESC_PREFIX) << 32) | (excl + agg));
             }
             if (lane == 0) {
                 s_base = excl;
+                s_agg = agg;
                 if (tile == ntiles - 1u) {
                     // Last tile: publish the new symbol count and advance the epoch.
                     const uint32_t total = excl + agg;
@@ -423,17 +515,15 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                     st->n[(e + 1u) & 1u] = LITERAL ? nnew : total;
                     st->epoch = e + 1u;
                 }
+                s_tile = atomicAdd(&st->ticket, 1u);  // next tile; read after barrier (D)
             }
         }
-        __syncthreads();
-        const uint32_t base = s_base;
-#pragma unroll
-        for (int j = 0; j < MC_ROWS; j++) {
-            uint32_t d = base + wsum[j * (MC_THREADS / 32) + warp] + lane_excl[j];
-#pragma unroll
-            for (int k = 0; k < 4; k++)
-                if (keep[j] & (1u << k)) dst[d++] = outv[j][k];
+        __syncthreads();  // (C) staged run, base and next ticket visible
+        {
+            const uint32_t base = s_base, cnt = s_agg;
+            for (uint32_t i = threadIdx.x; i < cnt; i += MC_THREADS) dst[base + i] = stage[i];
         }
+        __syncthreads();  // (D) stage and wsum may be reused
     }
 }
 

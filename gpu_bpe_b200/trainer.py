@@ -128,6 +128,11 @@ class TrainerSession:
         _lib.check(_lib.lib().b200bpe_trainer_last_run_ms(self._h, C.byref(ms)))
         return ms.value
 
+    def last_reset_ms(self) -> float:
+        ms = C.c_double()
+        _lib.check(_lib.lib().b200bpe_trainer_last_reset_ms(self._h, C.byref(ms)))
+        return ms.value
+
     def destroy(self):
         if self._h is not None:
             _lib.lib().b200bpe_trainer_destroy(self._h)

@@ -142,6 +142,8 @@ b200bpe_status b200bpe_trainer_pair_counts(b200bpe_trainer*, uint64_t* keys_out,
 b200bpe_status b200bpe_trainer_kernel_stats(b200bpe_trainer*, b200bpe_kernel_stats* out);
 /* Milliseconds of device time of the last b200bpe_trainer_run, by CUDA events on the library's stream. */
 b200bpe_status b200bpe_trainer_last_run_ms(b200bpe_trainer*, double* ms);
+/* Milliseconds of device time of the last b200bpe_trainer_reset (symbol tagging and buffer clears). */
+b200bpe_status b200bpe_trainer_last_reset_ms(b200bpe_trainer*, double* ms);
 void b200bpe_trainer_destroy(b200bpe_trainer*);
 
 /* ── trie: replaces compileVocabToTrie / parseHeader / parseTrieBuffers (src/bpe/tokenizer/trie.js:39,110,137) ──
