@@ -219,7 +219,7 @@ def main():
     ms_per_step = float(np.mean(step_ms))
     value = n_merges / (ms_per_step / 1e3)
     batches = (n_merges + 127) // 128
-    kernels_per_merge = 3 if world == 1 else 11
+    kernels_per_merge = (5 if mode == "literal" else 4) if world == 1 else 11
     gpu_launches = args.steps * (1 + batches * (1 + 128 * kernels_per_merge))
 
     # ── per-kernel device time: one more run with every kernel bracketed by CUDA events ──
@@ -235,10 +235,12 @@ def main():
         gbs = (nbytes / 1e9) / (ms_tot / 1e3) if ms_tot > 0 else 0.0
         kern[name] = {"ms_total": ms_tot, "launches": launches, "avg_us": 1e3 * ms_tot / max(1, launches),
                       "algorithmic_GB": nbytes / 1e9, "achieved_GBps": gbs, "frac_of_peak": gbs / peak}
+    kern["pair_count"]["skipped_launches"] = ks["pair_count_skipped_launches"]
+    kern["pair_count"]["skipped_ms_total"] = ks["pair_count_skipped_ms"]
     if world > 1:
         kern["exchange"] = {"ms_total": ks["exchange_ms"], "launches": ks["exchange_launches"],
                             "avg_us": 1e3 * ks["exchange_ms"] / max(1, ks["exchange_launches"])}
-    dom = max(("pair_count", "merge_compact"), key=lambda k: kern[k]["ms_total"])
+    dom = max(("pair_count", "argmax", "merge_compact"), key=lambda k: kern[k]["ms_total"])
     roofline = {"bound": "hbm", "kernel": "k_" + dom, "achieved": kern[dom]["achieved_GBps"], "peak": peak, "unit": "GB/s",
                 "frac": kern[dom]["frac_of_peak"], "traffic": None, "peak_source": peak_src,
                 "per_launch_algorithmic_bytes": kern[dom]["algorithmic_GB"] * 1e9 / max(1, kern[dom]["launches"]),

@@ -15,7 +15,7 @@ SYNTH_PATH = os.path.join(PKG, "libb200bpe_synth.so")
 u8p, u32p, u64p = C.POINTER(C.c_uint8), C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)
 
 COMPAT_LITERAL, COMPAT_FIXED = 0, 1
-FLAG_NO_GRAPH, FLAG_TIME_KERNELS = 1, 2
+FLAG_NO_GRAPH, FLAG_TIME_KERNELS, FLAG_FULL_RECOUNT = 1, 2, 4
 
 STATUS = {0: "OK", 1: "BAD_ARG", 2: "CUDA", 3: "NO_DEVICE", 4: "EMPTY_CORPUS", 5: "TABLE_FULL", 6: "LOOKBACK_TIMEOUT",
           7: "BAD_TRIE_MAGIC", 8: "BAD_TRIE_VERSION", 9: "TRUNCATED_TRIE", 10: "CAPACITY", 11: "NCCL", 12: "OOM",
@@ -38,7 +38,8 @@ class KernelStats(C.Structure):
     _fields_ = [("pair_count_ms", C.c_double), ("argmax_ms", C.c_double), ("merge_compact_ms", C.c_double),
                 ("exchange_ms", C.c_double), ("pair_count_launches", C.c_uint64), ("argmax_launches", C.c_uint64),
                 ("merge_compact_launches", C.c_uint64), ("exchange_launches", C.c_uint64),
-                ("pair_count_bytes", C.c_uint64), ("argmax_bytes", C.c_uint64), ("merge_compact_bytes", C.c_uint64)]
+                ("pair_count_bytes", C.c_uint64), ("argmax_bytes", C.c_uint64), ("merge_compact_bytes", C.c_uint64),
+                ("pair_count_skipped_ms", C.c_double), ("pair_count_skipped_launches", C.c_uint64)]
 
 
 PROGRESS_CB = C.CFUNCTYPE(None, C.POINTER(Progress), C.c_void_p)

@@ -50,7 +50,11 @@ struct DevState {
     uint32_t want_grow;     // arg-max saw the table more than half full
     uint32_t world;         // ranks sharing the job (1 = single GPU)
     unsigned long long best_packed;  // sharded runs: (count << 32) | ~pair32 after the all-reduce
-    uint32_t pad[8];
+    uint32_t incremental;   // 1 = the table is kept up to date by the merge kernel instead of being rebuilt per merge
+    uint32_t recount;       // incremental mode: the next merge must start with a full count into an empty table
+    uint32_t v_kept;        // symbols the last merge copied to the destination buffer
+    uint32_t tail_fix;      // literal + incremental: the tail fix-up kernel has work for the merge just applied
+    uint32_t pad[4];
 };
 
 struct CtaBest {

@@ -37,6 +37,7 @@ struct Trainer {
     uint32_t* d_sym_init = nullptr;
     bool own_inputs = true;
     bool has_mask = false;
+    bool incremental = false;  // table updated in place by the merge kernel (single GPU, unless FULL_RECOUNT)
     // working set
     uint32_t* buf[2] = {nullptr, nullptr};
     uint64_t cap_elems = 0;
@@ -48,6 +49,7 @@ struct Trainer {
     uint32_t* h_log = nullptr;    // pinned
     CtaBest* d_cta_best = nullptr;
     unsigned long long* d_desc = nullptr;
+    DeltaQueues dq{nullptr, nullptr, nullptr, 0, 0};  // incremental mode only
     Exchange xch;                 // sharded runs only
     cudaGraphExec_t graph = nullptr;
     uint32_t graph_iters = 0;
@@ -78,7 +80,7 @@ Trainer::~Trainer() {
     if (own_inputs) { cudaFree(d_bytes); cudaFree(d_mask); }
     cudaFree(d_sym_init);
     cudaFree(buf[0]); cudaFree(buf[1]); cudaFree(table); cudaFree(d_state); cudaFree(d_log);
-    cudaFree(d_cta_best); cudaFree(d_desc);
+    cudaFree(d_cta_best); cudaFree(d_desc); cudaFree(dq.minus); cudaFree(dq.plus); cudaFree(dq.counts);
     xch.release();
     if (h_state) cudaFreeHost(h_state);
     if (h_log) cudaFreeHost(h_log);
@@ -109,6 +111,17 @@ b200bpe_status Trainer::alloc_common() {
     B2_CUDA(cudaMalloc(&d_cta_best, sizeof(CtaBest) * (size_t)(sms * 4 + 1)));
     B2_CUDA(cudaMalloc(&d_desc, sizeof(unsigned long long) * (ntiles + 1)));
     B2_CUDA(cudaMemsetAsync(d_desc, 0, sizeof(unsigned long long) * (ntiles + 1), ctx->stream));
+    if (incremental) {
+        // one queue segment per CTA of the merge kernel; together about n0 / 2 entries per queue,
+        // which a merge only exceeds when it rewrites a large share of the corpus (then the
+        // overflow is applied to the table directly)
+        dq.segments = (uint32_t)grid_mc;
+        dq.seg_cap = (uint32_t)std::max<uint64_t>(1024, (n0 / 2) / dq.segments);
+        B2_CUDA(cudaMalloc(&dq.minus, (size_t)dq.seg_cap * dq.segments * 4));
+        B2_CUDA(cudaMalloc(&dq.plus, (size_t)dq.seg_cap * dq.segments * 4));
+        B2_CUDA(cudaMalloc(&dq.counts, (size_t)dq.segments * 8));
+        B2_CUDA(cudaMemsetAsync(dq.counts, 0, (size_t)dq.segments * 8, ctx->stream));
+    }
     B2_CUDA(cudaEventCreate(&ev_run0));
     B2_CUDA(cudaEventCreate(&ev_run1));
     B2_CUDA(cudaFuncSetAttribute(k_pair_count<PC_SLOTS, PC_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -138,12 +151,15 @@ b200bpe_status Trainer::init_state() {
     B2_CUDA(cudaMemsetAsync(table, 0, sizeof(PairSlot) << table_log2, s));
     // The look-back descriptors are tagged with the merge number, which restarts here.
     B2_CUDA(cudaMemsetAsync(d_desc, 0, sizeof(unsigned long long) * ((n0 + MC_TILE - 1) / MC_TILE + 1), s));
+    if (dq.counts) B2_CUDA(cudaMemsetAsync(dq.counts, 0, (size_t)dq.segments * 8, s));
     std::memset(h_state, 0, sizeof(DevState));
     h_state->n[0] = (uint32_t)n0;
     h_state->next_id = opts.first_token_id;
     h_state->table_log2 = table_log2;
     h_state->literal = (opts.compat_mode == B200BPE_COMPAT_LITERAL) ? 1u : 0u;
     h_state->world = (uint32_t)ctx->world;
+    h_state->incremental = incremental ? 1u : 0u;
+    h_state->recount = 1u;
     B2_CUDA(cudaMemcpyAsync(d_state, h_state, sizeof(DevState), cudaMemcpyHostToDevice, s));
     B2_CUDA(cudaEventRecord(ev_run1, s));
     B2_CUDA(cudaStreamSynchronize(s));
@@ -167,6 +183,7 @@ __global__ void k_clear_status(DevState* st, uint32_t table_log2) {
     st->status = DS_OK;
     st->want_grow = 0u;
     st->table_log2 = table_log2;
+    st->recount = 1u;  // the table is new and empty
 }
 
 // One merge iteration on the stream.  `timed` brackets each kernel with events.
@@ -197,8 +214,16 @@ b200bpe_status Trainer::enqueue_merge(int iter, bool timed) {
     }
     B2_CUDA(ev(3));
     dsync("argmax_setup");
-    if (literal) k_merge_compact<true><<<grid_mc, MC_THREADS, 0, s>>>(d_state, buf[0], buf[1], d_desc);
-    else k_merge_compact<false><<<grid_mc, MC_THREADS, 0, s>>>(d_state, buf[0], buf[1], d_desc);
+    if (incremental) {
+        if (literal) k_merge_compact<true, true><<<grid_mc, MC_THREADS, 0, s>>>(d_state, buf[0], buf[1], d_desc, table, dq);
+        else k_merge_compact<false, true><<<grid_mc, MC_THREADS, 0, s>>>(d_state, buf[0], buf[1], d_desc, table, dq);
+        k_apply_deltas<<<std::max(1, ctx->sm_count * 2), 256, 0, s>>>(d_state, dq, table);
+        if (literal) k_literal_tail<<<std::max(1, ctx->sm_count), 256, 0, s>>>(d_state, buf[0], buf[1], table);
+    } else if (literal) {
+        k_merge_compact<true, false><<<grid_mc, MC_THREADS, 0, s>>>(d_state, buf[0], buf[1], d_desc, table, dq);
+    } else {
+        k_merge_compact<false, false><<<grid_mc, MC_THREADS, 0, s>>>(d_state, buf[0], buf[1], d_desc, table, dq);
+    }
     B2_CUDA(ev(4));
     dsync("merge_compact");
     B2_CUDA(cudaGetLastError());
@@ -257,6 +282,7 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
     auto t0 = std::chrono::steady_clock::now();
     B2_CUDA(cudaEventRecord(ev_run0, s));
     int grow_retries = 0;
+    bool table_replaced = false;
     while (remaining > 0 && !early_stop) {
         const uint32_t batch = std::min(opts.batch_merges, remaining);
         const uint32_t before = merges_done;
@@ -281,13 +307,22 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
                 float ms = 0;
                 const size_t b = (size_t)i * 8;
                 const bool merged = i < got;
-                cudaEventElapsedTime(&ms, kev[b + 0], kev[b + 1]); stats.pair_count_ms += ms;
+                // In incremental mode the count kernel only works when a rebuild is due: at the very
+                // first merge, after a merge of two equal symbols, and after the table was replaced.
+                bool counted = true;
+                if (incremental) {
+                    const uint32_t g = before + i;
+                    counted = (g == 0) || (i == 0 && table_replaced) ||
+                              (g > 0 && i <= got && h_log[(size_t)(g - 1) * 4] == h_log[(size_t)(g - 1) * 4 + 1]);
+                }
+                cudaEventElapsedTime(&ms, kev[b + 0], kev[b + 1]);
+                if (counted) { stats.pair_count_ms += ms; stats.pair_count_launches++; stats.pair_count_bytes += 4ull * nk; }
+                else { stats.pair_count_skipped_ms += ms; stats.pair_count_skipped_launches++; }
                 cudaEventElapsedTime(&ms, kev[b + 1], kev[b + 2]); stats.exchange_ms += ms;
                 cudaEventElapsedTime(&ms, kev[b + 2], kev[b + 3]); stats.argmax_ms += ms;
                 cudaEventElapsedTime(&ms, kev[b + 3], kev[b + 4]); stats.merge_compact_ms += ms;
-                stats.pair_count_launches++; stats.argmax_launches++; stats.merge_compact_launches++;
+                stats.argmax_launches++; stats.merge_compact_launches++;
                 if (ctx->world > 1) stats.exchange_launches++;
-                stats.pair_count_bytes += 4ull * nk;
                 stats.argmax_bytes += 24ull << table_log2;
                 if (merged) {
                     const uint64_t nn = (ctx->world > 1) ? nk : nk - h_log[(size_t)(before + i) * 4 + 3];
@@ -310,9 +345,11 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
         remaining -= got;
         cur_n = h_state->n[h_state->epoch & 1];
         early_stop = h_state->early_stop != 0;
+        table_replaced = false;
         if (h_state->status == DS_TABLE_FULL || h_state->want_grow) {
             const bool was_full = h_state->status == DS_TABLE_FULL;
             b200bpe_status r = grow_table();
+            table_replaced = true;
             if (r) return r;
             if (was_full && ++grow_retries > 16) return B200BPE_ERR_TABLE_FULL;
         } else if (h_state->status == DS_LOOKBACK_TIMEOUT) {
@@ -374,6 +411,7 @@ static b200bpe_status make_trainer(b200bpe_ctx* c, const uint8_t* bytes, const u
     b200bpe_status r = check_opts(&c->c, opts, &t->opts);
     if (r) { delete t; return r; }
     t->merges_goal = t->opts.target_vocab_size - t->opts.first_token_id;
+    t->incremental = c->c.world == 1 && !(t->opts.flags & B200BPE_FLAG_FULL_RECOUNT);
     auto fail = [&](b200bpe_status st) { delete t; return st; };
     cudaStream_t s = c->c.stream;
     const size_t nb = std::max<uint64_t>(n, 1);
@@ -470,10 +508,16 @@ b200bpe_status b200bpe_trainer_pair_counts(b200bpe_trainer* h, uint64_t* keys_ou
     Trainer* t = h->t;
     B2_CUDA(cudaSetDevice(t->ctx->device));
     cudaStream_t s = t->ctx->stream;
+    B2_CUDA(cudaMemcpyAsync(t->h_state, t->d_state, sizeof(DevState), cudaMemcpyDeviceToHost, s));
+    B2_CUDA(cudaStreamSynchronize(s));
+    // An incrementally maintained table that is up to date is read out as it stands; otherwise
+    // the pairs are counted now and the table is left empty (with the rebuild still pending).
+    const bool as_is = t->incremental && t->h_state->recount == 0u;
     for (int attempt = 0; attempt < 12; attempt++) {
         k_begin_batch<<<1, 1, 0, s>>>(t->d_state, 0xFFFFFFFFu);
-        k_pair_count<PC_SLOTS, PC_THREADS><<<t->grid_pc, PC_THREADS, PC_SMEM_BYTES, s>>>(
-            t->d_state, t->buf[0], t->buf[1], t->table);
+        if (!as_is)
+            k_pair_count<PC_SLOTS, PC_THREADS><<<t->grid_pc, PC_THREADS, PC_SMEM_BYTES, s>>>(
+                t->d_state, t->buf[0], t->buf[1], t->table);
         PairSlot* tab = t->table;
         uint32_t tl2 = t->table_log2;
         if (t->ctx->world > 1) {
@@ -489,7 +533,7 @@ b200bpe_status b200bpe_trainer_pair_counts(b200bpe_trainer* h, uint64_t* keys_ou
         B2_CUDA(cudaMalloc(&dc, std::max<size_t>(4, (size_t)dcap * 4)));
         B2_CUDA(cudaMalloc(&dn, 4));
         B2_CUDA(cudaMemsetAsync(dn, 0, 4, s));
-        k_dump_table<<<t->ctx->sm_count * 4, 256, 0, s>>>(tab, 1u << tl2, dk, dc, dcap, dn);
+        k_dump_table<<<t->ctx->sm_count * 4, 256, 0, s>>>(tab, 1u << tl2, dk, dc, dcap, dn, as_is ? 0 : 1);
         if (tab != t->table) B2_CUDA(cudaMemsetAsync(t->table, 0, sizeof(PairSlot) << t->table_log2, s));
         uint32_t nd = 0;
         B2_CUDA(cudaMemcpyAsync(&nd, dn, 4, cudaMemcpyDeviceToHost, s));

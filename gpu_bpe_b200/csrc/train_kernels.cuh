@@ -103,7 +103,7 @@ k_pair_count(DevState* __restrict__ st, const uint32_t* __restrict__ buf0, const
     // One thread reads the stop flags for the whole CTA: `status` can change while this kernel
     // runs (another CTA may find the table full), and a CTA must not split at a barrier.
     __shared__ uint32_t s_idle;
-    if (threadIdx.x == 0) s_idle = st->early_stop | st->target_hit | st->status;
+    if (threadIdx.x == 0) s_idle = st->early_stop | st->target_hit | st->status | (st->incremental & (st->recount ^ 1u));
     for (int i = threadIdx.x; i < 2 * S; i += THREADS) skey[i] = 0u;
     __syncthreads();
     if (s_idle) return;
@@ -194,7 +194,8 @@ __device__ __forceinline__ void warp_best(uint32_t& c, unsigned long long& k) {
 // The merge set-up of the reference (train.wgsl:340-364) plus this library's batch control.
 __device__ __forceinline__ void setup_merge(DevState* st, uint32_t best_count, unsigned long long best_key,
                                             uint32_t* __restrict__ log) {
-    if (st->status != DS_OK) { st->active = 0; return; }
+    st->tail_fix = 0u;
+    if (st->status != DS_OK) { st->active = 0u; st->recount = 1u; return; }
     if (best_count < 2u || st->next_id > TOKEN_MASK) {
         st->early_stop = 1u;
         st->active = 0u;
@@ -210,6 +211,10 @@ __device__ __forceinline__ void setup_merge(DevState* st, uint32_t best_count, u
     st->k3_epoch = st->epoch;
     st->ticket = 0u;
     st->active = 1u;
+    // Incremental table: a merge of two equal symbols collapses whole runs, which the local
+    // update rule does not cover; the table is emptied and rebuilt by a full count instead.
+    st->recount = st->incremental ? (a == b ? 1u : 0u) : 1u;
+    st->tail_fix = (st->incremental && st->literal && a != b) ? 1u : 0u;
 }
 
 // mode 0: single GPU — finish with setup_merge.
@@ -225,10 +230,11 @@ k_argmax_setup(DevState* __restrict__ st, PairSlot* __restrict__ table, CtaBest*
     // Neither flag changes before every CTA has passed this test: only the last CTA to finish
     // writes them.  Once the run has stopped, nothing is left for the merge kernel to apply.
     if (st->early_stop | st->target_hit) {
-        if (blockIdx.x == 0 && threadIdx.x == 0) st->active = 0u;
+        if (blockIdx.x == 0 && threadIdx.x == 0) { st->active = 0u; st->tail_fix = 0u; }
         return;
     }
     const uint32_t C = 1u << st->table_log2;
+    const bool clear = st->incremental == 0u;  // an incrementally maintained table is never wiped here
     uint4* __restrict__ t4 = reinterpret_cast<uint4*>(table);
     uint32_t bc = 0, occ = 0;
     unsigned long long bk = 0ull;
@@ -238,7 +244,7 @@ k_argmax_setup(DevState* __restrict__ st, PairSlot* __restrict__ table, CtaBest*
         if (key != 0ull) {
             occ++;
             if (is_better(q.z, key, bc, bk)) { bc = q.z; bk = key; }
-            __stcg(t4 + i, make_uint4(0u, 0u, 0u, 0u));
+            if (clear) __stcg(t4 + i, make_uint4(0u, 0u, 0u, 0u));
         }
     }
     warp_best(bc, bk);
@@ -343,6 +349,142 @@ __device__ __forceinline__ uint32_t lookback(const unsigned long long* __restric
     }
 }
 
+// Incremental table maintenance, the rare path of k_merge_compact: called by a whole warp for a row
+// in which some pair merges.  Every lane rebuilds an 8-symbol window (left neighbour, its four
+// symbols, the next three), finds which of its four (t, t+1) pairs change, and appends the old
+// pair to the "minus" queue and the new one to the "plus" queue; k_apply_deltas folds the queues
+// into the table afterwards.  With a != b matches never overlap, so the symbol after a dropped one
+// is always kept and this window is enough.  A full queue falls back to updating the table here.
+// Each CTA of the merge kernel appends to its own segment of the queues (segment g = CTA g), so the
+// reservation counters are never shared between CTAs.
+struct DeltaQueues {
+    uint32_t* minus;    // segments of (left << 16 | right) keys to take out once each
+    uint32_t* plus;     // segments of keys to put in once each
+    uint32_t* counts;   // per segment: entries reserved in minus, in plus (2 words)
+    uint32_t seg_cap;   // entries per segment
+    uint32_t segments;  // number of segments = CTAs of the merge kernel
+};
+
+__device__ __noinline__ void queue_deltas(DevState* st, PairSlot* __restrict__ table, DeltaQueues dq, uint32_t s0, uint4 own,
+                                          uint32_t s5, uint32_t y31, uint32_t z31, uint32_t i0, uint32_t N, bool interior,
+                                          uint32_t A, uint32_t B, uint32_t NW, int lane, uint32_t logC) {
+    uint32_t s[8] = {s0, own.x, own.y, own.z, own.w, s5, 0u, 0u};
+    s[6] = __shfl_down_sync(0xFFFFFFFFu, own.y, 1);
+    s[7] = __shfl_down_sync(0xFFFFFFFFu, own.z, 1);
+    if (lane == 31) { s[6] = y31; s[7] = z31; }
+    uint32_t left = 0u, right = 0u, live = 0xFFu;
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        left |= ((s[k] & TOKEN_MASK) == A ? 1u : 0u) << k;
+        right |= ((s[k] & (TOKEN_MASK | WORD_START_BIT)) == B ? 1u : 0u) << k;
+    }
+    if (!interior) {
+        live = (i0 >= 1u ? 1u : 0u);
+#pragma unroll
+        for (int k = 1; k < 8; k++) live |= (i0 + k - 1u < N ? 1u : 0u) << k;
+    }
+    const uint32_t m = left & (right >> 1) & live & (live >> 1);  // bit k: pair (s[k], s[k+1]) merges, k = 0..6
+    const uint32_t touched = (m | (m << 1) | (m >> 1)) & 0x1Eu & live;
+    uint32_t km[4], kp[4], vm = 0u, vp = 0u;
+#pragma unroll
+    for (int t = 1; t <= 4; t++) {
+        km[t - 1] = kp[t - 1] = 0u;
+        if (!((touched >> t) & 1u)) continue;
+        // the old pair (s[t], s[t+1]) leaves the table if it was a counted pair
+        const uint32_t lo = s[t] & TOKEN_MASK, ro = s[t + 1] & TOKEN_MASK;
+        if (((live >> (t + 1)) & 1u) && !(s[t + 1] & WORD_START_BIT) && lo != 0u && ro != 0u) {
+            km[t - 1] = (lo << 16) | ro;
+            vm |= 1u << (t - 1);
+        }
+        // the new pair whose left symbol is t, unless t itself is dropped
+        if (!((m >> (t - 1)) & 1u)) {
+            const bool mt = (m >> t) & 1u;
+            // the right symbol of a match is dropped, so the neighbour is then t + 2
+            const uint32_t sr = mt ? s[t + 2] : s[t + 1];
+            const bool mr = mt ? ((m >> (t + 2)) & 1u) : ((m >> (t + 1)) & 1u);
+            const bool lr = mt ? ((live >> (t + 2)) & 1u) : ((live >> (t + 1)) & 1u);
+            if ((mt || mr) && lr && !(sr & WORD_START_BIT)) {
+                const uint32_t ln = mt ? NW : lo, rn = mr ? NW : (sr & TOKEN_MASK);
+                if (ln != 0u && rn != 0u) {
+                    kp[t - 1] = (ln << 16) | rn;
+                    vp |= 1u << (t - 1);
+                }
+            }
+        }
+    }
+    // reserve room in both queues: one atomic per queue per warp
+    const uint32_t cm = __popc(vm), cp = __popc(vp);
+    uint32_t im = cm, ip = cp;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t a = __shfl_up_sync(0xFFFFFFFFu, im, o), b = __shfl_up_sync(0xFFFFFFFFu, ip, o);
+        if (lane >= o) { im += a; ip += b; }
+    }
+    uint32_t base_m = 0u, base_p = 0u;
+    if (lane == 31) {
+        if (im) base_m = atomicAdd(&dq.counts[2u * blockIdx.x], im);
+        if (ip) base_p = atomicAdd(&dq.counts[2u * blockIdx.x + 1u], ip);
+    }
+    base_m = __shfl_sync(0xFFFFFFFFu, base_m, 31) + im - cm;
+    base_p = __shfl_sync(0xFFFFFFFFu, base_p, 31) + ip - cp;
+    uint32_t* __restrict__ seg_m = dq.minus + (size_t)blockIdx.x * dq.seg_cap;
+    uint32_t* __restrict__ seg_p = dq.plus + (size_t)blockIdx.x * dq.seg_cap;
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        if ((vm >> t) & 1u) {
+            if (base_m < dq.seg_cap) seg_m[base_m] = km[t];
+            else {
+                const unsigned long long key = ((unsigned long long)(km[t] >> 16) << 32) | (km[t] & 0xFFFFu);
+                table_add(table, logC, key, hash_pair(key), 0xFFFFFFFFu, st);
+            }
+            base_m++;
+        }
+        if ((vp >> t) & 1u) {
+            if (base_p < dq.seg_cap) seg_p[base_p] = kp[t];
+            else {
+                const unsigned long long key = ((unsigned long long)(kp[t] >> 16) << 32) | (kp[t] & 0xFFFFu);
+                table_add(table, logC, key, hash_pair(key), 1u, st);
+            }
+            base_p++;
+        }
+    }
+}
+
+// Fold the delta queues of the merge just applied into the table, one CTA per segment at a time.
+// Equal keys held by the lanes of a warp are combined first (match-any), so a popular neighbour
+// pair costs one atomic per warp.  A segment's counters are cleared by the CTA that consumed it.
+__global__ void __launch_bounds__(256)
+k_apply_deltas(DevState* __restrict__ st, DeltaQueues dq, PairSlot* __restrict__ table) {
+    const uint32_t logC = st->table_log2;
+    const int lane = threadIdx.x & 31;
+    for (uint32_t g = blockIdx.x; g < dq.segments; g += gridDim.x) {
+        const uint32_t nm = min(dq.counts[2u * g], dq.seg_cap), np = min(dq.counts[2u * g + 1u], dq.seg_cap);
+        const uint32_t total = nm + np;
+        if (total == 0u) continue;
+        const uint32_t* __restrict__ seg_m = dq.minus + (size_t)g * dq.seg_cap;
+        const uint32_t* __restrict__ seg_p = dq.plus + (size_t)g * dq.seg_cap;
+        for (uint32_t base = 0; base < total; base += blockDim.x) {
+            const uint32_t i = base + threadIdx.x;
+            const bool on = i < total;
+            const bool neg = i < nm;
+            const uint32_t k32 = on ? (neg ? seg_m[i] : seg_p[i - nm]) : 0u;
+            // same key and same sign within the warp → one add of the group's size
+            const unsigned long long tagk = ((unsigned long long)(neg ? 1u : 0u) << 32) | k32;
+            const uint32_t act = __ballot_sync(0xFFFFFFFFu, on);
+            if (on) {
+                const uint32_t peers = __match_any_sync(act, tagk);
+                if (lane == __ffs(peers) - 1) {
+                    const unsigned long long key = ((unsigned long long)(k32 >> 16) << 32) | (k32 & 0xFFFFu);
+                    const uint32_t c = __popc(peers);
+                    table_add(table, logC, key, hash_pair(key), neg ? (0u - c) : c, st);
+                }
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) { dq.counts[2u * g] = 0u; dq.counts[2u * g + 1u] = 0u; }
+    }
+}
+
 // One tile = 4096 symbols; warp w owns the 512 consecutive symbols [w * 512, (w + 1) * 512) of the
 // tile as four 16-byte rows per lane, so a warp's kept symbols are contiguous in the output.
 // Per tile: load, decide per symbol (rewritten? dropped?), rank within the warp, publish the
@@ -350,14 +492,22 @@ __device__ __forceinline__ uint32_t lookback(const unsigned long long* __restric
 // warp 0 looks back for the tile's global offset, then copy the staged run out with coalesced
 // stores.  Tiles are handed out by an atomic ticket so that a waiting tile's predecessors are
 // always running.
-template <bool LITERAL>
-__global__ void __launch_bounds__(MC_THREADS, 6)
-k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsigned long long* __restrict__ desc) {
+//
+// INCR: the pair table is kept up to date instead of being rebuilt by a full count for the next
+// merge.  Every position whose pair with its right neighbour changes takes the old pair out and
+// puts the new one in (a handful of atomics per merged occurrence).  This needs `a != b` (matches
+// cannot overlap, so a dropped symbol's successor is always kept and three symbols of look-ahead
+// settle everything); a merge with a == b collapses whole runs (train.wgsl:482-497 on a run
+// "aaaa" yields one symbol), so it empties the table here and the next merge counts from scratch.
+template <bool LITERAL, bool INCR>
+__global__ void __launch_bounds__(MC_THREADS, INCR ? 5 : 6)
+k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsigned long long* __restrict__ desc,
+                PairSlot* __restrict__ table, DeltaQueues dq) {
     __shared__ uint32_t stage[MC_TILE];
     __shared__ uint32_t wsum[MC_WARPS];
     __shared__ uint32_t s_tile, s_base, s_agg;
-    // `active`, `k3_epoch`, `n[k3_epoch & 1]`, `a`, `b`, `new_id` and `max_count` are written by the
-    // set-up step only, so every thread of every CTA of this launch reads the same values.
+    // `active`, `k3_epoch`, `n[k3_epoch & 1]`, `a`, `b`, `new_id`, `max_count` and `recount` are written
+    // by the set-up step only, so every thread of every CTA of this launch reads the same values.
     if (!st->active) return;
     const uint32_t e = st->k3_epoch;
     const uint32_t N = st->n[e & 1];
@@ -369,6 +519,8 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
     const uint32_t tag = (e + 1u) & 0x3FFFFFFFu;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint4* src4 = reinterpret_cast<const uint4*>(src);
+    const bool deltas = INCR && st->recount == 0u;
+    const uint32_t logC = st->table_log2;
 
     if (threadIdx.x == 0) s_tile = atomicAdd(&st->ticket, 1u);
     __syncthreads();
@@ -383,39 +535,54 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
             const uint32_t v = vwarp + j * 32 + lane;
             q[j] = (4u * v < N) ? src4[v] : make_uint4(0u, 0u, 0u, 0u);
         }
-        // the symbols just outside the warp's span come from global memory
-        uint32_t edge_prev = 0u, edge_next = 0u;
+        // the symbols just outside the warp's span come from global memory: one before, up to three after
+        uint32_t edge_prev = 0u, edge_n0 = 0u, edge_n1 = 0u, edge_n2 = 0u;
         {
             const uint32_t i0 = 4u * vwarp, i1 = 4u * (vwarp + MC_ROWS * 32);
             if (lane == 0) edge_prev = (i0 > 0u && i0 - 1u < N) ? src[i0 - 1u] : 0u;
-            if (lane == 31) edge_next = (i1 < N) ? src[i1] : 0u;
+            if (lane == 31) {
+                edge_n0 = (i1 < N) ? src[i1] : 0u;
+                if (INCR) {
+                    edge_n1 = (i1 + 1u < N) ? src[i1 + 1u] : 0u;
+                    edge_n2 = (i1 + 2u < N) ? src[i1 + 2u] : 0u;
+                }
+            }
+            if (LITERAL) {
+                // A symbol owned by another thread may already carry this merge's in-place rewrite;
+                // the new id is fresh, so mapping it back to `a` restores the snapshot.
+                if ((edge_prev & TOKEN_MASK) == NW) edge_prev = (edge_prev & WORD_START_BIT) | A;
+                if ((edge_n0 & TOKEN_MASK) == NW) edge_n0 = (edge_n0 & WORD_START_BIT) | A;
+                if ((edge_n1 & TOKEN_MASK) == NW) edge_n1 = (edge_n1 & WORD_START_BIT) | A;
+                if ((edge_n2 & TOKEN_MASK) == NW) edge_n2 = (edge_n2 & WORD_START_BIT) | A;
+            }
         }
         // row-crossing neighbours: lane 0 needs the previous row's lane 31, lane 31 the next row's lane 0
-        uint32_t first_x[MC_ROWS], last_w[MC_ROWS];
+        uint32_t last_w[MC_ROWS], first_x[MC_ROWS], first_y[MC_ROWS], first_z[MC_ROWS];
 #pragma unroll
         for (int j = 0; j < MC_ROWS; j++) {
-            first_x[j] = __shfl_sync(0xFFFFFFFFu, q[j].x, 0);
             last_w[j] = __shfl_sync(0xFFFFFFFFu, q[j].w, 31);
+            first_x[j] = __shfl_sync(0xFFFFFFFFu, q[j].x, 0);
+            if (INCR) {
+                first_y[j] = __shfl_sync(0xFFFFFFFFu, q[j].y, 0);
+                first_z[j] = __shfl_sync(0xFFFFFFFFu, q[j].z, 0);
+            }
         }
         uint32_t keep = 0u;        // 4 bits per row
         uint32_t rank[MC_ROWS];    // tile-local rank of this lane's first kept symbol of row j, within the warp
         uint32_t run = 0u;         // kept symbols of the warp's earlier rows
-        // A warp whose whole span (and the symbol after it) lies below both N and the compaction
-        // limit needs no bounds tests.
-        const bool interior = 4u * (vwarp + MC_ROWS * 32) < min(N, limit);
+        // A warp whose whole span (and the three symbols after it) lies below both N and the
+        // compaction limit needs no bounds tests.
+        const bool interior = 4u * (vwarp + MC_ROWS * 32) + 3u < min(N, limit);  // incl. the look-ahead of the delta path
 #pragma unroll
         for (int j = 0; j < MC_ROWS; j++) {
-            uint32_t pv = __shfl_up_sync(0xFFFFFFFFu, q[j].w, 1);
-            uint32_t nx = __shfl_down_sync(0xFFFFFFFFu, q[j].x, 1);
-            if (lane == 0) pv = j > 0 ? last_w[j > 0 ? j - 1 : 0] : edge_prev;
-            if (lane == 31) nx = j < MC_ROWS - 1 ? first_x[j < MC_ROWS - 1 ? j + 1 : j] : edge_next;
-            if (LITERAL) {
-                // A neighbour owned by another thread may already carry this merge's in-place
-                // rewrite; the new id is fresh, so mapping it back to `a` restores the snapshot.
-                if ((pv & TOKEN_MASK) == NW) pv = (pv & WORD_START_BIT) | A;
-                if ((nx & TOKEN_MASK) == NW) nx = (nx & WORD_START_BIT) | A;
-            }
-            const uint32_t s[6] = {pv, q[j].x, q[j].y, q[j].z, q[j].w, nx};
+            const uint32_t i0 = 4u * (vwarp + j * 32 + lane);
+            // s[0] = left neighbour, s[1..4] = own symbols, s[5] = right neighbour
+            uint32_t s[6];
+            s[0] = __shfl_up_sync(0xFFFFFFFFu, q[j].w, 1);
+            s[1] = q[j].x; s[2] = q[j].y; s[3] = q[j].z; s[4] = q[j].w;
+            s[5] = __shfl_down_sync(0xFFFFFFFFu, q[j].x, 1);
+            if (lane == 0) s[0] = j > 0 ? last_w[j > 0 ? j - 1 : 0] : edge_prev;
+            if (lane == 31) s[5] = j < MC_ROWS - 1 ? first_x[j < MC_ROWS - 1 ? j + 1 : j] : edge_n0;
             // left[k]: s[k] is `a`; right[k]: s[k] is `b` and does not start a word.  A pair matches at
             // k when left[k] & right[k + 1]; the symbol at k + 1 is then dropped (train.wgsl:482-497).
             uint32_t left = 0u, right = 0u;
@@ -424,32 +591,45 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                 left |= ((s[k] & TOKEN_MASK) == A ? 1u : 0u) << k;
                 right |= ((s[k] & (TOKEN_MASK | WORD_START_BIT)) == B ? 1u : 0u) << k;
             }
-            uint32_t match = left & (right >> 1);           // bit k: pair (k, k + 1) merges; k = 0 is the left neighbour
-            uint32_t kb;
-            if (interior) {
-                kb = ~match & 15u;                          // own symbol k (bit k + 1 of s) is dropped iff match bit k
-                match = (match >> 1) & 15u;                 // own symbol k is rewritten iff pair (k + 1, k + 2) of s matches
-            } else {
-                const uint32_t i0 = 4u * (vwarp + j * 32 + lane);
-                uint32_t live = 0u, pairable = 0u, below = 0u;
+            uint32_t m = left & (right >> 1);   // bit k: pair (s[k], s[k+1]) merges, k = 0..4
+            uint32_t live = 0x3Fu;              // bit k: s[k] is a live position (bit 0: i0 >= 1; bit k >= 1: i0 + k - 1 < N)
+            if (!interior) {
+                live = (i0 >= 1u ? 1u : 0u);
 #pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    live |= (i0 + k < N ? 1u : 0u) << k;
-                    pairable |= (i0 + k + 1u < N ? 1u : 0u) << k;
-                    below |= (i0 + k < limit ? 1u : 0u) << k;
+                for (int k = 1; k < 6; k++) live |= (i0 + k - 1u < N ? 1u : 0u) << k;
+                m &= live & (live >> 1);
+            }
+            // own symbol t (t = 1..4): dropped iff m[t-1], rewritten iff m[t]
+            uint32_t kb = ~m & 15u;             // bit t-1 of kb ↔ own symbol t kept
+            const uint32_t rew = (m >> 1) & 15u;
+            if (!interior) {
+                uint32_t below = 0u;
+#pragma unroll
+                for (int k = 0; k < 4; k++) below |= (i0 + k < limit ? 1u : 0u) << k;
+                kb &= (live >> 1) & below;
+            }
+            if (INCR && deltas) {
+                // The pair (t, t+1) changes iff one of the pairs at t-1, t, t+1 merges.  For lanes 0..30
+                // those are matches some lane of this row sees in its own window; lane 31 also has to
+                // look at the two pairs that begin in the next row (or outside the warp's span).
+                uint32_t y = 0u, z = 0u;
+                bool far = false;
+                if (lane == 31) {
+                    y = j < MC_ROWS - 1 ? first_y[j < MC_ROWS - 1 ? j + 1 : j] : edge_n1;
+                    z = j < MC_ROWS - 1 ? first_z[j < MC_ROWS - 1 ? j + 1 : j] : edge_n2;
+                    const bool ly = interior || i0 + 5u < N, lz = interior || i0 + 6u < N;
+                    far = (ly && (s[5] & TOKEN_MASK) == A && (y & (TOKEN_MASK | WORD_START_BIT)) == B) ||
+                          (lz && (y & TOKEN_MASK) == A && (z & (TOKEN_MASK | WORD_START_BIT)) == B);
                 }
-                // a match needs both symbols live: own pairs by `pairable`, the left neighbour's pair by own bit 0
-                const uint32_t m_own = (match >> 1) & pairable;
-                const uint32_t m_prev = (match & 1u) & live;
-                kb = ~((m_own << 1) | m_prev) & live & below & 15u;
-                match = m_own;
+                if (__any_sync(0xFFFFFFFFu, m != 0u || far))
+                    queue_deltas(st, table, dq, s[0], q[j], s[5], y, z, i0, N, interior, A, B, NW, lane, logC);
             }
             uint32_t ov[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
 #pragma unroll
             for (int k = 0; k < 4; k++) {
-                if ((match >> k) & 1u) {
+                if ((rew >> k) & 1u) {
                     ov[k] = NW | (ov[k] & WORD_START_BIT);
-                    if (LITERAL) src[4u * (vwarp + j * 32 + lane) + k] = ov[k];  // the reference rewrites the source in place
+                    if (LITERAL) src[i0 + k] = ov[k];  // the reference rewrites the source in place
                 }
             }
             q[j] = make_uint4(ov[0], ov[1], ov[2], ov[3]);
@@ -513,6 +693,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                     if (!LITERAL && total != nnew && st->status == DS_OK && st->world == 1u)
                         atomicExch(&st->status, (uint32_t)DS_INTERNAL);
                     st->n[(e + 1u) & 1u] = LITERAL ? nnew : total;
+                    st->v_kept = total;
                     st->epoch = e + 1u;
                 }
                 s_tile = atomicAdd(&st->ticket, 1u);  // next tile; read after barrier (D)
@@ -525,6 +706,55 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
         }
         __syncthreads();  // (D) stage and wsum may be reused
     }
+    if (INCR && !deltas) {
+        // a == b (or a rebuild is already due): no deltas were written, so nobody else touches the
+        // table during this launch; empty it for the full count that the next merge starts with.
+        uint4* __restrict__ t4 = reinterpret_cast<uint4*>(table);
+        const uint32_t C = 1u << logC;
+        for (uint32_t i = blockIdx.x * MC_THREADS + threadIdx.x; i < C; i += gridDim.x * MC_THREADS)
+            t4[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+
+// Literal mode with an incrementally maintained table: k_merge_compact accounts for the merge as
+// if every kept symbol had been copied; the reference, however, copies only the inputs below
+// limit = N - count and leaves older contents in the rest of the destination (train.wgsl:698,727).
+// This kernel takes out the pairs of the symbols that were not copied and puts in the pairs of
+// what the destination holds instead.  src = the merge's source buffer after its in-place
+// rewrites, dst = its destination; V = symbols copied, N1 = the new symbol count.
+__global__ void __launch_bounds__(256)
+k_literal_tail(DevState* __restrict__ st, const uint32_t* buf0, const uint32_t* buf1, PairSlot* __restrict__ table) {
+    // runs right after k_merge_compact of the same merge: k3_epoch is that merge, epoch already advanced
+    if (!st->tail_fix) return;
+    const uint32_t e = st->k3_epoch;
+    const uint32_t N = st->n[e & 1], N1 = st->n[(e + 1u) & 1u], V = st->v_kept;
+    const uint32_t* __restrict__ src = (e & 1) ? buf1 : buf0;
+    const uint32_t* __restrict__ dst = (e & 1) ? buf0 : buf1;
+    const uint32_t B = st->b, NW = st->new_id, limit = N - st->max_count;
+    const uint32_t logC = st->table_log2;
+    auto counted = [](uint32_t l, uint32_t r) { return !(r & WORD_START_BIT) && (l & TOKEN_MASK) != 0u && (r & TOKEN_MASK) != 0u; };
+    auto emit = [&](uint32_t l, uint32_t r, uint32_t delta) {
+        const unsigned long long key = ((unsigned long long)(l & TOKEN_MASK) << 32) | (r & TOKEN_MASK);
+        table_add(table, logC, key, hash_pair(key), delta, st);
+    };
+    // a position of the source is dropped iff its left neighbour was rewritten to the new symbol
+    auto dropped = [&](uint32_t i) { return i > 0u && i < N && (src[i - 1u] & TOKEN_MASK) == NW && !(src[i] & WORD_START_BIT) &&
+                                            (src[i] & TOKEN_MASK) == B; };
+    const uint32_t gtid = blockIdx.x * blockDim.x + threadIdx.x, gstride = gridDim.x * blockDim.x;
+    // (1) pairs whose left symbol is a kept source position >= limit: they were counted, but never copied
+    for (uint32_t i = limit + gtid; i < N; i += gstride) {
+        if (dropped(i)) continue;
+        const uint32_t r = (i + 1u < N && dropped(i + 1u)) ? i + 2u : i + 1u;
+        if (r < N && counted(src[i], src[r])) emit(src[i], src[r], 0xFFFFFFFFu);
+    }
+    // (2) the pair that joined the last copied symbol to the first kept source position >= limit
+    if (gtid == 0 && V > 0u) {
+        const uint32_t z0 = dropped(limit) ? limit + 1u : limit;
+        if (z0 < N && counted(dst[V - 1u], src[z0])) emit(dst[V - 1u], src[z0], 0xFFFFFFFFu);
+    }
+    // (3) the pairs of what the destination really holds from the last copied symbol on
+    for (uint32_t u = (V > 0u ? V - 1u : 0u) + gtid; u + 1u < N1; u += gstride)
+        if (counted(dst[u], dst[u + 1u])) emit(dst[u], dst[u + 1u], 1u);
 }
 
 // ─────────────────────────────── symbol buffer set-up ───────────────────────────────
@@ -563,15 +793,17 @@ k_tag_symbols(const uint8_t* __restrict__ bytes, const uint8_t* __restrict__ mas
     }
 }
 
-// Copy the non-empty slots of the table out (and empty them), for tests.
+// Copy the pairs with a non-zero count out (and optionally empty the table), for tests.
 __global__ void k_dump_table(PairSlot* table, uint32_t C, unsigned long long* keys, uint32_t* counts, uint32_t cap,
-                             uint32_t* n_out) {
+                             uint32_t* n_out, int clear) {
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < C; i += gridDim.x * blockDim.x) {
         const unsigned long long k = table[i].key;
         if (k) {
-            const uint32_t d = atomicAdd(n_out, 1u);
-            if (d < cap) { keys[d] = k; counts[d] = table[i].count; }
-            table[i].key = 0ull; table[i].count = 0u;
+            if (table[i].count != 0u) {  // pairs whose count went back to 0 stay in an incremental table as dead keys
+                const uint32_t d = atomicAdd(n_out, 1u);
+                if (d < cap) { keys[d] = k; counts[d] = table[i].count; }
+            }
+            if (clear) { table[i].key = 0ull; table[i].count = 0u; }
         }
     }
 }

@@ -50,7 +50,10 @@ enum {
 
 enum {
     B200BPE_FLAG_NO_GRAPH = 1u,      /* launch kernels one by one instead of one CUDA graph per batch */
-    B200BPE_FLAG_TIME_KERNELS = 2u   /* bracket every kernel with CUDA events (implies NO_GRAPH) */
+    B200BPE_FLAG_TIME_KERNELS = 2u,  /* bracket every kernel with CUDA events (implies NO_GRAPH) */
+    B200BPE_FLAG_FULL_RECOUNT = 4u   /* rebuild the pair table with a full count before every merge, as the
+                                        reference does (train.wgsl:196-202,376-431), instead of updating it in
+                                        place around the merged occurrences; the merge list is the same */
 };
 
 typedef struct b200bpe_ctx b200bpe_ctx;
@@ -83,9 +86,12 @@ typedef void (*b200bpe_progress_cb)(const b200bpe_progress*, void* user);
 typedef struct {
     double pair_count_ms, argmax_ms, merge_compact_ms, exchange_ms;
     uint64_t pair_count_launches, argmax_launches, merge_compact_launches, exchange_launches;
-    uint64_t pair_count_bytes;    /* 4 * N_k summed over merges */
+    uint64_t pair_count_bytes;    /* 4 * N_k summed over the merges that counted */
     uint64_t argmax_bytes;        /* 2 * 12 * table slots per merge (scan + clear) */
     uint64_t merge_compact_bytes; /* 4 * N_k + 4 * N_{k+1} summed over merges */
+    /* launches of the count kernel that had nothing to do because the table was up to date */
+    double pair_count_skipped_ms;
+    uint64_t pair_count_skipped_launches;
 } b200bpe_kernel_stats;
 
 const char* b200bpe_status_str(b200bpe_status);

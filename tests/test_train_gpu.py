@@ -157,3 +157,38 @@ def test_trainer_api_mirror(engine):
     with pytest.raises(ValueError, match="No symbols to train on"):
         BPETrainer(engine).train(b"")
     assert "# Total tokens: 466" in tr.exportVocab()
+
+
+@pytest.mark.parametrize("mode", ["literal", "fixed"])
+def test_incrementally_maintained_table_stays_exact(engine, mode):
+    """By default the pair table is updated in place around each merged occurrence; after any
+    number of merges it must equal a fresh count of the live symbols."""
+    _, _, sym = small_text(2, 23, 2 << 20)
+    s = TrainerSession.from_symbols(engine, sym, target_vocab_size=256 + 400, compat_mode=mode)
+    done = 0
+    for step in (1, 2, 37, 128, 200):
+        s.run(step - done if step > done else 0)
+        done = step
+        got = {((k >> 32) << 16) | (k & 0xFFFF): v for k, v in s.pair_counts().items()}
+        assert got == O.pair_counts(s.symbols()), (mode, step)
+    s.destroy()
+
+
+@pytest.mark.parametrize("mode", ["literal", "fixed"])
+def test_full_recount_and_incremental_agree(engine, mode):
+    _, _, sym = small_text(1, 6, 1 << 20)
+    want = O.train(sym, 300, mode, threads=8)
+    a = run_gpu(engine, sym, 300, mode)
+    b = run_gpu(engine, sym, 300, mode, flags=_lib.FLAG_FULL_RECOUNT)
+    assert a == b
+    assert a[0] == want["merges"].tolist() and a[2] == want["symbols"].tolist()
+
+
+def test_incremental_with_frequent_equal_symbol_merges(engine):
+    """Tiny alphabets make a == b merges common; each one forces a rebuild of the table."""
+    rng = np.random.default_rng(123)
+    sym = random_symbols(rng, 150_000, alphabet=3, p_ws=0.05)
+    for mode in ("literal", "fixed"):
+        want = O.train(sym, 120, mode, threads=4)
+        got = run_gpu(engine, sym, 120, mode)
+        assert got[0] == want["merges"].tolist() and got[2] == want["symbols"].tolist()
