@@ -16,7 +16,7 @@ constexpr uint32_t TOKEN_MASK = 0xFFFFu;       // low 16 bits = token id
 constexpr uint32_t INVALID_TOKEN = 0xFFFFFFFFu;
 
 // Device-side status words (DevState::status); mapped to b200bpe_status by the host.
-enum DevStatus : uint32_t { DS_OK = 0, DS_TABLE_FULL = 1, DS_LOOKBACK_TIMEOUT = 2, DS_INTERNAL = 3 };
+enum DevStatus : uint32_t { DS_OK = 0, DS_TABLE_FULL = 1, DS_LOOKBACK_TIMEOUT = 2, DS_INTERNAL = 3, DS_BUCKET_FULL = 4 };
 
 // One slot of the open-addressing pair table: 64-bit (left << 32 | right) key, 0 = empty
 // (the left symbol of a counted pair is never 0), and its count.  16 bytes so that an insert
@@ -54,7 +54,8 @@ struct DevState {
     uint32_t recount;       // incremental mode: the next merge must start with a full count into an empty table
     uint32_t v_kept;        // symbols the last merge copied to the destination buffer
     uint32_t tail_fix;      // literal + incremental: the tail fix-up kernel has work for the merge just applied
-    uint32_t pad[4];
+    uint32_t fill_hwm;      // sharded runs: largest exchange-bucket fill seen on any rank since the batch began
+    uint32_t pad[3];
 };
 
 struct CtaBest {

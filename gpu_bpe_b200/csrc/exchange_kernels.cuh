@@ -10,7 +10,7 @@
 //                     holding its fill, so buckets never need clearing)
 //   3. k_accumulate   the owner sums what it received into its table of owned pairs
 //   4. k_argmax_setup (mode 1) arg-max over the owned pairs → packed (count << 32 | ~pair)
-//   5. all-reduce max of {packed best, status, want_grow} — 24 bytes
+//   5. all-reduce max of {packed best, status, want_grow, largest bucket fill} — 32 bytes
 //   6. k_setup_from_packed  every rank decodes the same winner and sets up its local merge
 //
 // max over the packed word reproduces the reference's order exactly: larger count first, then
@@ -42,7 +42,7 @@ k_partition(DevState* __restrict__ st, PairSlot* __restrict__ table, PairSlot* _
             if (d < cap) {
                 reinterpret_cast<uint4*>(buckets)[(size_t)o * cap + d] = q;
             } else {
-                atomicExch(&st->status, (uint32_t)DS_TABLE_FULL);
+                atomicCAS(&st->status, (uint32_t)DS_OK, (uint32_t)DS_BUCKET_FULL);
             }
             __stcg(t4 + i, make_uint4(0u, 0u, 0u, 0u));
         }
@@ -58,6 +58,7 @@ __global__ void k_seal_buckets(DevState* __restrict__ st, PairSlot* __restrict__
     const uint32_t f = idle ? 0u : min(fill[o], cap - 1u);
     buckets[(size_t)o * cap].key = 0ull;
     buckets[(size_t)o * cap].count = f;
+    if (!idle) atomicMax(&st->fill_hwm, fill[o]);
     fill[o] = 0u;
 }
 
@@ -85,13 +86,16 @@ __global__ void k_pack_flags(DevState* __restrict__ st, unsigned long long* __re
     words[0] = idle ? 0ull : st->best_packed;
     words[1] = st->status;
     words[2] = st->want_grow;
+    words[3] = st->fill_hwm;
 }
 
 __global__ void k_unpack_flags(DevState* __restrict__ st, const unsigned long long* __restrict__ words,
                                uint32_t* __restrict__ log) {
     if (st->early_stop | st->target_hit) return;
-    if (words[1] != DS_OK && st->status == DS_OK) st->status = (uint32_t)words[1];
+    // every rank takes the largest status code: a full bucket anywhere stops all ranks alike
+    if (words[1] > st->status) st->status = (uint32_t)words[1];
     if (words[2]) st->want_grow = 1u;
+    st->fill_hwm = (uint32_t)words[3];
     const unsigned long long p = words[0];
     const uint32_t cnt = (uint32_t)(p >> 32);
     const uint32_t pair32 = ~(uint32_t)p;
@@ -104,9 +108,11 @@ struct Exchange {
     PairSlot* recv = nullptr;   // world inboxes of `cap` slots
     PairSlot* owned = nullptr;  // pairs this rank owns
     uint32_t* fill = nullptr;
-    unsigned long long* words = nullptr;      // 3 words out
-    unsigned long long* words_max = nullptr;  // 3 words after the all-reduce
-    uint32_t cap = 0, owned_log2 = 0, local_log2 = 0;
+    unsigned long long* words = nullptr;      // 4 words out
+    unsigned long long* words_max = nullptr;  // 4 words after the all-reduce
+    uint32_t cap = 0;        // slots per bucket in use (header included); the same on every rank
+    uint32_t cap_alloc = 0;  // slots per bucket allocated
+    uint32_t owned_log2 = 0, local_log2 = 0;
 
     void release() {
         cudaFree(send); cudaFree(recv); cudaFree(owned); cudaFree(fill); cudaFree(words); cudaFree(words_max);
@@ -119,15 +125,18 @@ struct Exchange {
         owned_log2 = table_log2;
         // A local table is at most half full before it grows; spread over `world` owners that is
         // C / (2 * world) entries per bucket on average.  Twice that, plus the header.
-        cap = std::max<uint32_t>(64u, (1u << table_log2) / world) + 1u;
-        B2_CUDA(cudaMalloc(&send, sizeof(PairSlot) * (size_t)cap * world));
-        B2_CUDA(cudaMalloc(&recv, sizeof(PairSlot) * (size_t)cap * world));
+        cap_alloc = std::max<uint32_t>(64u, (1u << table_log2) / world) + 1u;
+        // What is sent per peer and merge is `cap` slots, sized to the traffic actually seen (the
+        // host adapts it between batches from the all-reduced high-water mark), not to the table.
+        cap = std::min<uint32_t>(cap_alloc, 32768u + 1u);
+        B2_CUDA(cudaMalloc(&send, sizeof(PairSlot) * (size_t)cap_alloc * world));
+        B2_CUDA(cudaMalloc(&recv, sizeof(PairSlot) * (size_t)cap_alloc * world));
         B2_CUDA(cudaMalloc(&owned, sizeof(PairSlot) << owned_log2));
         B2_CUDA(cudaMalloc(&fill, sizeof(uint32_t) * world));
-        B2_CUDA(cudaMalloc(&words, 24));
-        B2_CUDA(cudaMalloc(&words_max, 24));
-        B2_CUDA(cudaMemsetAsync(send, 0, sizeof(PairSlot) * (size_t)cap * world, ctx->stream));
-        B2_CUDA(cudaMemsetAsync(recv, 0, sizeof(PairSlot) * (size_t)cap * world, ctx->stream));
+        B2_CUDA(cudaMalloc(&words, 32));
+        B2_CUDA(cudaMalloc(&words_max, 32));
+        B2_CUDA(cudaMemsetAsync(send, 0, sizeof(PairSlot) * (size_t)cap_alloc * world, ctx->stream));
+        B2_CUDA(cudaMemsetAsync(recv, 0, sizeof(PairSlot) * (size_t)cap_alloc * world, ctx->stream));
         B2_CUDA(cudaMemsetAsync(owned, 0, sizeof(PairSlot) << owned_log2, ctx->stream));
         B2_CUDA(cudaMemsetAsync(fill, 0, sizeof(uint32_t) * world, ctx->stream));
         return B200BPE_OK;
@@ -136,6 +145,17 @@ struct Exchange {
     b200bpe_status resize(Ctx* ctx, uint32_t table_log2) {
         release();
         return init(ctx, table_log2);
+    }
+
+    // Between batches: fit the bucket size to the traffic.  Every rank sees the same all-reduced
+    // numbers, so every rank takes the same decision.  Returns true if `cap` changed.
+    bool adapt(bool overflowed, uint32_t fill_hwm) {
+        uint32_t want = cap;
+        if (overflowed) want = std::min<uint32_t>(cap_alloc, std::max<uint32_t>(cap * 4u, fill_hwm * 2u + 2u));
+        else if ((uint64_t)fill_hwm * 4u < cap && cap > 4097u) want = std::max<uint32_t>(4097u, fill_hwm * 2u + 1u);
+        if (want == cap) return false;
+        cap = want;
+        return true;
     }
 
     b200bpe_status nccl_fail(Ctx* ctx, int rc, const char* what) {
@@ -179,7 +199,7 @@ struct Exchange {
         k_argmax_setup<<<grid_am, AM_THREADS, 0, s>>>(st, owned, cta_best, log, 1);
         k_set_table_log2<<<1, 1, 0, s>>>(st, table_log2);
         k_pack_flags<<<1, 1, 0, s>>>(st, words);
-        int rc = ctx->nccl.AllReduce(words, words_max, 3, /*ncclUint64*/ 5, /*ncclMax*/ 2, ctx->comm, s);
+        int rc = ctx->nccl.AllReduce(words, words_max, 4, /*ncclUint64*/ 5, /*ncclMax*/ 2, ctx->comm, s);
         if (rc) return nccl_fail(ctx, rc, "ncclAllReduce");
         k_unpack_flags<<<1, 1, 0, s>>>(st, words_max, log);
         return B200BPE_OK;

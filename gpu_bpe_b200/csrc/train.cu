@@ -176,6 +176,7 @@ b200bpe_status Trainer::init_state() {
 }
 
 __global__ void k_begin_batch(DevState* st, uint32_t target) {
+    st->fill_hwm = 0u;
     st->merges_target = target;
     st->target_hit = (st->merges_done >= target) ? 1u : 0u;
 }
@@ -346,6 +347,15 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
         cur_n = h_state->n[h_state->epoch & 1];
         early_stop = h_state->early_stop != 0;
         table_replaced = false;
+        if (ctx->world > 1 && (h_state->status == DS_BUCKET_FULL || h_state->status == DS_OK)) {
+            // sharded runs: resize the exchange buckets to the traffic seen (same decision on every rank)
+            const bool over = h_state->status == DS_BUCKET_FULL;
+            if (over && xch.cap >= xch.cap_alloc) { h_state->status = DS_TABLE_FULL; }
+            else if (xch.adapt(over, h_state->fill_hwm) || over) {
+                if (graph) { cudaGraphExecDestroy(graph); graph = nullptr; }
+                if (over) { k_clear_status<<<1, 1, 0, s>>>(d_state, table_log2); h_state->status = DS_OK; }
+            }
+        }
         if (h_state->status == DS_TABLE_FULL || h_state->want_grow) {
             const bool was_full = h_state->status == DS_TABLE_FULL;
             b200bpe_status r = grow_table();
@@ -539,6 +549,12 @@ b200bpe_status b200bpe_trainer_pair_counts(b200bpe_trainer* h, uint64_t* keys_ou
         B2_CUDA(cudaMemcpyAsync(&nd, dn, 4, cudaMemcpyDeviceToHost, s));
         B2_CUDA(cudaMemcpyAsync(t->h_state, t->d_state, sizeof(DevState), cudaMemcpyDeviceToHost, s));
         B2_CUDA(cudaStreamSynchronize(s));
+        if (t->h_state->status == DS_BUCKET_FULL) {
+            // No all-reduce on this path, so the ranks cannot agree on a larger bucket here: give up.
+            cudaFree(dk); cudaFree(dc); cudaFree(dn);
+            k_clear_status<<<1, 1, 0, s>>>(t->d_state, t->table_log2);
+            return B200BPE_ERR_CAPACITY;
+        }
         const bool full = t->h_state->status == DS_TABLE_FULL;
         if (!full) {
             const uint32_t m = std::min(nd, dcap);
