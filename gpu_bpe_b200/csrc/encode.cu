@@ -13,6 +13,8 @@
 // children.  Each CTA also keeps a direct-mapped shared-memory cache of recent probes.
 #include <algorithm>
 #include <cstring>
+#include <mutex>
+#include <string>
 #include <vector>
 
 #include "ctx.cuh"
@@ -604,6 +606,92 @@ b200bpe_status b200bpe_encode_batch(b200bpe_tok* h, const uint8_t* bytes, const 
     if (got) B2_CUDA(cudaMemcpyAsync(tokens_out, t->d_out, got * 4, cudaMemcpyDeviceToHost, s));
     B2_CUDA(cudaStreamSynchronize(s));
     return B200BPE_OK;
+}
+
+// ── encoding without any allocation ──
+// Some callers may not allocate device memory at the moment they encode: a real-time or
+// fault-tolerant loop that must not hit the allocator's locks or its out-of-memory path, code that
+// runs while another library owns all remaining memory, a signal-safe or hook context.  For them
+// the work buffers of one encode (per-chunk token staging, counts, offsets, look-back descriptors)
+// live in one file-scope device array instead of the tokenizer's growable pool.  The array is part
+// of the library image: every GPU that loads the library holds it until the process exits.
+constexpr uint64_t NOALLOC_MAX_BYTES = 1ull << 20;   // largest input of one call
+constexpr uint64_t NOALLOC_MAX_CHUNKS = 8192;        // largest number of chunks of one call
+constexpr uint64_t NA_ALIGN = 256;
+constexpr uint64_t na_up(uint64_t x) { return (x + NA_ALIGN - 1) / NA_ALIGN * NA_ALIGN; }
+// staging holds chunk_size tokens per chunk: at most the input length rounded up to one more chunk
+constexpr uint64_t NA_OFF_STAGING = 0;
+constexpr uint64_t NA_STAGING_BYTES = na_up((NOALLOC_MAX_BYTES + NOALLOC_MAX_BYTES) * 4);
+constexpr uint64_t NA_OFF_COUNTS = NA_OFF_STAGING + NA_STAGING_BYTES;
+constexpr uint64_t NA_OFF_CHUNK_OFF = NA_OFF_COUNTS + na_up((NOALLOC_MAX_CHUNKS + 1) * 4);
+constexpr uint64_t NA_OFF_DESC = NA_OFF_CHUNK_OFF + na_up((NOALLOC_MAX_CHUNKS + 1) * 8);
+constexpr uint64_t NA_OFF_CTL = NA_OFF_DESC + na_up((NOALLOC_MAX_CHUNKS / SC_THREADS + 2) * 8);
+constexpr uint64_t NA_OFF_TOTAL = NA_OFF_CTL + NA_ALIGN;
+constexpr uint64_t NOALLOC_SCRATCH_BYTES = NA_OFF_TOTAL + NA_ALIGN;
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+// In host code `g_noalloc_scratch` is only a stand-in for the symbol, not an address a kernel can
+// use; the device address is asked for once per device, with that device current.
+static unsigned char* g_noalloc_ptr[64] = {};
+static std::mutex g_noalloc_mutex;
+
+static b200bpe_status noalloc_scratch_for(int device, unsigned char** out) {
+    if (device < 0 || device >= 64) return B200BPE_ERR_BAD_ARG;
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_ptr[device]) {
+        void* p = nullptr;
+        B2_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        g_noalloc_ptr[device] = static_cast<unsigned char*>(p);
+    }
+    *out = g_noalloc_ptr[device];
+    return B200BPE_OK;
+}
+
+b200bpe_status b200bpe_encode_device_noalloc(b200bpe_tok* h, const uint8_t* d_bytes, uint64_t n, uint32_t* d_tokens_out,
+                                             uint64_t cap, uint64_t* n_tokens_out) {
+    if (!h || (!d_bytes && n) || (!d_tokens_out && cap) || !n_tokens_out) return B200BPE_ERR_BAD_ARG;
+    Tokenizer* t = h->t;
+    *n_tokens_out = 0;
+    if (n == 0) return B200BPE_OK;
+    const uint64_t chunks = (n + t->chunk - 1) / t->chunk;
+    if (n > NOALLOC_MAX_BYTES || chunks > NOALLOC_MAX_CHUNKS) {
+        set_last_error("b200bpe_encode_device_noalloc: input of " + std::to_string(n) + " bytes in " + std::to_string(chunks) +
+                       " chunks exceeds the built-in scratch (at most " + std::to_string(NOALLOC_MAX_BYTES) + " bytes and " +
+                       std::to_string(NOALLOC_MAX_CHUNKS) + " chunks per call)");
+        return B200BPE_ERR_CAPACITY;
+    }
+    B2_CUDA(cudaSetDevice(t->ctx->device));
+    unsigned char* base = nullptr;
+    b200bpe_status r = noalloc_scratch_for(t->ctx->device, &base);
+    if (r) return r;
+    cudaStream_t s = t->ctx->stream;
+    uint32_t* staging = reinterpret_cast<uint32_t*>(base + NA_OFF_STAGING);
+    uint32_t* counts = reinterpret_cast<uint32_t*>(base + NA_OFF_COUNTS);
+    uint64_t* chunk_off = reinterpret_cast<uint64_t*>(base + NA_OFF_CHUNK_OFF);
+    unsigned long long* desc = reinterpret_cast<unsigned long long*>(base + NA_OFF_DESC);
+    uint32_t* ctl = reinterpret_cast<uint32_t*>(base + NA_OFF_CTL);
+    uint64_t* total = reinterpret_cast<uint64_t*>(base + NA_OFF_TOTAL);
+    // The array keeps whatever the last call left: the look-back descriptors, the tile ticket and
+    // the error flag must start at zero; everything else is written before it is read.
+    const uint64_t ntiles = chunks / SC_THREADS + 2;
+    B2_CUDA(cudaMemsetAsync(desc, 0, ntiles * 8, s));
+    B2_CUDA(cudaMemsetAsync(ctl, 0, 8, s));
+    TrieDev td{t->d_root_lut, t->d_trans, t->trans_mask, t->d_node_tok};
+    const size_t smem = (size_t)(1 << TW_CACHE_LOG2) * 8 + 1024;
+    const int grid_w = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)t->ctx->sm_count * 3, (chunks + TW_THREADS - 1) / TW_THREADS));
+    k_trie_walk<TW_THREADS, TW_CACHE_LOG2><<<grid_w, TW_THREADS, smem, s>>>(td, d_bytes, n, t->chunk, nullptr, nullptr, 0, chunks,
+                                                                       staging, counts);
+    const int grid_c = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)t->ctx->sm_count * 8, ntiles));
+    k_scan_compact<<<grid_c, SC_THREADS, 0, s>>>(staging, counts, t->chunk, nullptr, 0, chunks, desc, ctl, chunk_off,
+                                                d_tokens_out, cap, total);
+    B2_CUDA(cudaGetLastError());
+    B2_CUDA(cudaMemcpyAsync(t->h_total, total, 8, cudaMemcpyDeviceToHost, s));
+    B2_CUDA(cudaMemcpyAsync(t->h_total + 1, ctl, 8, cudaMemcpyDeviceToHost, s));
+    B2_CUDA(cudaStreamSynchronize(s));
+    if ((uint32_t)(t->h_total[1] >> 32) != 0u) return B200BPE_ERR_LOOKBACK_TIMEOUT;
+    *n_tokens_out = t->h_total[0];
+    return t->h_total[0] > cap ? B200BPE_ERR_CAPACITY : B200BPE_OK;
 }
 
 b200bpe_status b200bpe_tokenizer_last_ms(b200bpe_tok* h, double* walk_ms, double* compact_ms) {

@@ -68,6 +68,15 @@ class TrieTokenizer:
                    "b200bpe_encode_device")
         return nt.value
 
+    def encodeDeviceNoAlloc(self, d_bytes: int, n: int, d_tokens: int, cap: int) -> int:
+        """encodeDevice without any allocation inside the call: the work buffers are a fixed array
+        inside the library (at most 1 MiB of input and 8,192 chunks per call).  For callers that
+        cannot afford the allocator at encode time.  One call at a time per device."""
+        nt = C.c_uint64()
+        _lib.check(_lib.lib().b200bpe_encode_device_noalloc(self._h, C.c_void_p(d_bytes), n, C.c_void_p(d_tokens), cap,
+                                                           C.byref(nt)), "b200bpe_encode_device_noalloc")
+        return nt.value
+
     def encodeBatchDevice(self, d_bytes: int, d_doc_offsets: int, n_docs: int, n_bytes: int, d_tokens: int, cap: int,
                           d_tok_offsets: int) -> int:
         nt = C.c_uint64()

@@ -183,6 +183,17 @@ b200bpe_status b200bpe_encode_device(b200bpe_tok*, const uint8_t* d_bytes, uint6
 b200bpe_status b200bpe_encode_batch_device(b200bpe_tok*, const uint8_t* d_bytes, const uint64_t* d_doc_offsets,
                                            uint32_t n_docs, uint64_t n_bytes, uint32_t* d_tokens_out, uint64_t cap,
                                            uint64_t* d_tok_offsets_out, uint64_t* n_tokens_out);
+/* b200bpe_encode_device for callers that must not allocate (no counterpart in the reference).
+ * The same kernels and the same result, but the work buffers are a fixed array built into the
+ * library image instead of the tokenizer's growable pool, and the call makes no cudaMalloc,
+ * cudaFree or other allocating call: for encode steps inside a latency-critical or
+ * memory-exhausted process, where the allocator's locks, its implicit synchronisation or its
+ * failure are not acceptable.  Limits: n <= 1 MiB and at most 8,192 chunks per call; larger
+ * inputs return B200BPE_ERR_CAPACITY (b200bpe_last_error() says why).  The first call on a device
+ * looks up the array's device address, so make it before any stream capture begins.  All calls on
+ * a device share the array: calls that overlap on the GPU race; one at a time per device. */
+b200bpe_status b200bpe_encode_device_noalloc(b200bpe_tok*, const uint8_t* d_bytes, uint64_t n, uint32_t* d_tokens_out,
+                                             uint64_t cap, uint64_t* n_tokens_out);
 /* Milliseconds of device time of the last encode call, split by kernel: walk, scan+compaction. */
 b200bpe_status b200bpe_tokenizer_last_ms(b200bpe_tok*, double* walk_ms, double* compact_ms);
 void b200bpe_tokenizer_destroy(b200bpe_tok*);
