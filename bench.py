@@ -237,6 +237,9 @@ def main():
                       "algorithmic_GB": nbytes / 1e9, "achieved_GBps": gbs, "frac_of_peak": gbs / peak}
     kern["pair_count"]["skipped_launches"] = ks["pair_count_skipped_launches"]
     kern["pair_count"]["skipped_ms_total"] = ks["pair_count_skipped_ms"]
+    kern["table_update"] = {"ms_total": ks["table_update_ms"], "launches": ks["merge_compact_launches"],
+                            "avg_us": 1e3 * ks["table_update_ms"] / max(1, ks["merge_compact_launches"]),
+                            "what": "k_apply_deltas + k_literal_tail"}
     if world > 1:
         kern["exchange"] = {"ms_total": ks["exchange_ms"], "launches": ks["exchange_launches"],
                             "avg_us": 1e3 * ks["exchange_ms"] / max(1, ks["exchange_launches"])}

@@ -39,7 +39,8 @@ class KernelStats(C.Structure):
                 ("exchange_ms", C.c_double), ("pair_count_launches", C.c_uint64), ("argmax_launches", C.c_uint64),
                 ("merge_compact_launches", C.c_uint64), ("exchange_launches", C.c_uint64),
                 ("pair_count_bytes", C.c_uint64), ("argmax_bytes", C.c_uint64), ("merge_compact_bytes", C.c_uint64),
-                ("pair_count_skipped_ms", C.c_double), ("pair_count_skipped_launches", C.c_uint64)]
+                ("pair_count_skipped_ms", C.c_double), ("pair_count_skipped_launches", C.c_uint64),
+                ("table_update_ms", C.c_double)]
 
 
 PROGRESS_CB = C.CFUNCTYPE(None, C.POINTER(Progress), C.c_void_p)

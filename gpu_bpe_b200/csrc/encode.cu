@@ -307,6 +307,7 @@ struct Tokenizer {
     uint32_t* d_root_lut = nullptr;
     uint2* d_trans = nullptr;
     uint32_t trans_mask = 0;
+    size_t trans_bytes = 0;
     uint32_t* d_node_tok = nullptr;
     // pooled work buffers (grown on demand, as tokenizer.js:108-166 does)
     uint8_t* d_in = nullptr; uint64_t in_cap = 0;
@@ -363,6 +364,7 @@ struct Tokenizer {
     b200bpe_status launch(const uint8_t* d_bytes, uint64_t n, const uint64_t* d_docs, uint32_t n_docs,
                           uint32_t* d_tokens, uint64_t cap, uint64_t* d_tok_offsets) {
         cudaStream_t s = ctx->stream;
+        set_persisting_window(ctx, d_trans, trans_bytes);  // keep the transition table resident in L2
         const uint64_t max_chunks = (n + chunk - 1) / chunk + (d_docs ? n_docs : 0);
         b200bpe_status r = ensure_work(std::max<uint64_t>(1, max_chunks));
         if (r) return r;
@@ -493,23 +495,7 @@ b200bpe_status b200bpe_tokenizer_create(b200bpe_ctx* c, const void* trie, size_t
     for (auto& e : t->ev) B2_TRY(cudaEventCreate(&e));
     B2_TRY(cudaFuncSetAttribute(k_trie_walk<TW_THREADS, TW_CACHE_LOG2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (1 << TW_CACHE_LOG2) * 8 + 1024));
-    // Keep the transition table resident in L2: a persisting access-policy window on the stream.
-    {
-        int max_win = 0;
-        cudaDeviceGetAttribute(&max_win, cudaDevAttrMaxAccessPolicyWindowSize, c->c.device);
-        const size_t bytes = std::min<size_t>(trans.size() * 8, (size_t)std::max(0, max_win));
-        if (bytes > 0) {
-            cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, std::min<size_t>(bytes, 32u << 20));
-            cudaStreamAttrValue attr{};
-            attr.accessPolicyWindow.base_ptr = t->d_trans;
-            attr.accessPolicyWindow.num_bytes = bytes;
-            attr.accessPolicyWindow.hitRatio = 1.0f;
-            attr.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
-            attr.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
-            cudaStreamSetAttribute(s, cudaStreamAttributeAccessPolicyWindow, &attr);
-            cudaGetLastError();
-        }
-    }
+    t->trans_bytes = trans.size() * 8;
     B2_TRY(cudaStreamSynchronize(s));
 #undef B2_TRY
     *out = new b200bpe_tok{t};

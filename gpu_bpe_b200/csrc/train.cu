@@ -107,7 +107,7 @@ b200bpe_status Trainer::alloc_common() {
     grid_pc = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)sms * PC_CTAS_PER_SM, (nvec + PC_THREADS - 1) / PC_THREADS));
     grid_am = std::max(1, std::min(sms * 4, (int)((1u << table_log2) / (AM_THREADS * 4))));
     const uint64_t ntiles = (n0 + MC_TILE - 1) / MC_TILE;
-    grid_mc = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)sms * 8, ntiles));
+    grid_mc = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)sms * 3, ntiles));
     B2_CUDA(cudaMalloc(&d_cta_best, sizeof(CtaBest) * (size_t)(sms * 4 + 1)));
     B2_CUDA(cudaMalloc(&d_desc, sizeof(unsigned long long) * (ntiles + 1)));
     B2_CUDA(cudaMemsetAsync(d_desc, 0, sizeof(unsigned long long) * (ntiles + 1), ctx->stream));
@@ -126,6 +126,10 @@ b200bpe_status Trainer::alloc_common() {
     B2_CUDA(cudaEventCreate(&ev_run1));
     B2_CUDA(cudaFuncSetAttribute(k_pair_count<PC_SLOTS, PC_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  PC_SMEM_BYTES));
+    B2_CUDA(cudaFuncSetAttribute(k_merge_compact<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_SMEM_BYTES));
+    B2_CUDA(cudaFuncSetAttribute(k_merge_compact<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_SMEM_BYTES));
+    B2_CUDA(cudaFuncSetAttribute(k_merge_compact<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_SMEM_BYTES));
+    B2_CUDA(cudaFuncSetAttribute(k_merge_compact<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_SMEM_BYTES));
     if (ctx->world > 1) {
         b200bpe_status s = xch.init(ctx, table_log2);
         if (s) return s;
@@ -216,15 +220,17 @@ b200bpe_status Trainer::enqueue_merge(int iter, bool timed) {
     B2_CUDA(ev(3));
     dsync("argmax_setup");
     if (incremental) {
-        if (literal) k_merge_compact<true, true><<<grid_mc, MC_THREADS, 0, s>>>(d_state, buf[0], buf[1], d_desc, table, dq);
-        else k_merge_compact<false, true><<<grid_mc, MC_THREADS, 0, s>>>(d_state, buf[0], buf[1], d_desc, table, dq);
+        if (literal) k_merge_compact<true, true><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, table, dq);
+        else k_merge_compact<false, true><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, table, dq);
+        B2_CUDA(ev(5));
         k_apply_deltas<<<std::max(1, ctx->sm_count * 2), 256, 0, s>>>(d_state, dq, table);
         if (literal) k_literal_tail<<<std::max(1, ctx->sm_count), 256, 0, s>>>(d_state, buf[0], buf[1], table);
     } else if (literal) {
-        k_merge_compact<true, false><<<grid_mc, MC_THREADS, 0, s>>>(d_state, buf[0], buf[1], d_desc, table, dq);
+        k_merge_compact<true, false><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, table, dq);
     } else {
-        k_merge_compact<false, false><<<grid_mc, MC_THREADS, 0, s>>>(d_state, buf[0], buf[1], d_desc, table, dq);
+        k_merge_compact<false, false><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, table, dq);
     }
+    if (!incremental) B2_CUDA(ev(5));
     B2_CUDA(ev(4));
     dsync("merge_compact");
     B2_CUDA(cudaGetLastError());
@@ -321,7 +327,8 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
                 else { stats.pair_count_skipped_ms += ms; stats.pair_count_skipped_launches++; }
                 cudaEventElapsedTime(&ms, kev[b + 1], kev[b + 2]); stats.exchange_ms += ms;
                 cudaEventElapsedTime(&ms, kev[b + 2], kev[b + 3]); stats.argmax_ms += ms;
-                cudaEventElapsedTime(&ms, kev[b + 3], kev[b + 4]); stats.merge_compact_ms += ms;
+                cudaEventElapsedTime(&ms, kev[b + 3], kev[b + 5]); stats.merge_compact_ms += ms;
+                cudaEventElapsedTime(&ms, kev[b + 5], kev[b + 4]); stats.table_update_ms += ms;
                 stats.argmax_launches++; stats.merge_compact_launches++;
                 if (ctx->world > 1) stats.exchange_launches++;
                 stats.argmax_bytes += 24ull << table_log2;

@@ -25,8 +25,11 @@ constexpr int PC_LOCAL_PROBES = 2;   // linear probes in shared memory before go
 constexpr int TABLE_MAX_PROBE = 1024;
 constexpr int AM_THREADS = 256;
 constexpr int MC_THREADS = 256;
-constexpr int MC_ROWS = 4;                               // uint4 rows per thread
-constexpr int MC_TILE = MC_THREADS * 4 * MC_ROWS;        // 4096 symbols per tile
+constexpr int MC_ROWS = 4;                               // uint4 rows per thread per sub-tile
+constexpr int MC_SUB = MC_THREADS * 4 * MC_ROWS;         // 4,096 symbols per sub-tile
+constexpr int MC_SUBS = 4;                               // sub-tiles per tile
+constexpr int MC_TILE = MC_SUB * MC_SUBS;                // 16,384 symbols per tile: one look-back each
+constexpr int MC_SMEM_BYTES = MC_TILE * 4;               // staging area (dynamic shared memory)
 constexpr int MC_WARPS = MC_THREADS / 32;
 constexpr uint32_t LOOKBACK_MAX_SPINS = 1u << 22;        // bounded wait; then DS_LOOKBACK_TIMEOUT
 
@@ -238,13 +241,23 @@ k_argmax_setup(DevState* __restrict__ st, PairSlot* __restrict__ table, CtaBest*
     uint4* __restrict__ t4 = reinterpret_cast<uint4*>(table);
     uint32_t bc = 0, occ = 0;
     unsigned long long bk = 0ull;
-    for (uint32_t i = blockIdx.x * AM_THREADS + threadIdx.x; i < C; i += gridDim.x * AM_THREADS) {
-        const uint4 q = __ldcg(t4 + i);
-        const unsigned long long key = ((unsigned long long)q.y << 32) | q.x;
-        if (key != 0ull) {
-            occ++;
-            if (is_better(q.z, key, bc, bk)) { bc = q.z; bk = key; }
-            if (clear) __stcg(t4 + i, make_uint4(0u, 0u, 0u, 0u));
+    // four independent 16-byte loads in flight per thread: the scan is latency-bound otherwise
+    const uint32_t stride = gridDim.x * AM_THREADS;
+    for (uint32_t i0 = blockIdx.x * AM_THREADS + threadIdx.x; i0 < C; i0 += 4u * stride) {
+        uint4 q[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const uint32_t i = i0 + u * stride;
+            q[u] = i < C ? __ldcg(t4 + i) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const unsigned long long key = ((unsigned long long)q[u].y << 32) | q[u].x;
+            if (key != 0ull) {
+                occ++;
+                if (is_better(q[u].z, key, bc, bk)) { bc = q[u].z; bk = key; }
+                if (clear) __stcg(t4 + i0 + u * stride, make_uint4(0u, 0u, 0u, 0u));
+            }
         }
     }
     warp_best(bc, bk);
@@ -485,13 +498,17 @@ k_apply_deltas(DevState* __restrict__ st, DeltaQueues dq, PairSlot* __restrict__
     }
 }
 
-// One tile = 4096 symbols; warp w owns the 512 consecutive symbols [w * 512, (w + 1) * 512) of the
-// tile as four 16-byte rows per lane, so a warp's kept symbols are contiguous in the output.
-// Per tile: load, decide per symbol (rewritten? dropped?), rank within the warp, publish the
-// tile's kept count, stage the kept symbols in shared memory at their tile-local rank while
-// warp 0 looks back for the tile's global offset, then copy the staged run out with coalesced
-// stores.  Tiles are handed out by an atomic ticket so that a waiting tile's predecessors are
-// always running.
+// One tile = 16,384 symbols, worked through as four sub-tiles of 4,096: in a sub-tile warp w owns
+// the 512 consecutive symbols [w * 512, (w + 1) * 512) as four 16-byte rows per lane, so a warp's
+// kept symbols are contiguous in the output.  Per sub-tile: load, decide per symbol (rewritten?
+// dropped?), rank within the warp, and stage the kept symbols in shared memory right behind those
+// of the sub-tiles before it.  Per tile: publish the kept count, look back for the tile's global
+// offset (warp 0), copy the staged run out with coalesced stores.  Tiles are handed out by an
+// atomic ticket so that a waiting tile's predecessors are always running.
+//
+// Why four sub-tiles: the tiles of a launch move in waves, a wave resolves its offsets front to
+// back at one look-back window (32 tiles) per L2 round trip, and that chain, not HBM, bounds the
+// kernel when a tile is small.  One look-back per 64 KB of input moves the bound out of the way.
 //
 // INCR: the pair table is kept up to date instead of being rebuilt by a full count for the next
 // merge.  Every position whose pair with its right neighbour changes takes the old pair out and
@@ -500,12 +517,12 @@ k_apply_deltas(DevState* __restrict__ st, DeltaQueues dq, PairSlot* __restrict__
 // settle everything); a merge with a == b collapses whole runs (train.wgsl:482-497 on a run
 // "aaaa" yields one symbol), so it empties the table here and the next merge counts from scratch.
 template <bool LITERAL, bool INCR>
-__global__ void __launch_bounds__(MC_THREADS, INCR ? 5 : 6)
+__global__ void __launch_bounds__(MC_THREADS, 3)
 k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsigned long long* __restrict__ desc,
                 PairSlot* __restrict__ table, DeltaQueues dq) {
-    __shared__ uint32_t stage[MC_TILE];
-    __shared__ uint32_t wsum[MC_WARPS];
-    __shared__ uint32_t s_tile, s_base, s_agg;
+    extern __shared__ __align__(16) uint32_t stage[];  // MC_TILE words
+    __shared__ uint32_t wsum[2][MC_WARPS];
+    __shared__ uint32_t s_tile, s_next, s_base;
     // `active`, `k3_epoch`, `n[k3_epoch & 1]`, `a`, `b`, `new_id`, `max_count` and `recount` are written
     // by the set-up step only, so every thread of every CTA of this launch reads the same values.
     if (!st->active) return;
@@ -522,161 +539,203 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
     const bool deltas = INCR && st->recount == 0u;
     const uint32_t logC = st->table_log2;
 
-    if (threadIdx.x == 0) s_tile = atomicAdd(&st->ticket, 1u);
-    __syncthreads();
-    for (;;) {
-        const uint32_t tile = s_tile;
-        if (tile >= ntiles) break;
-        const uint32_t vwarp = tile * (MC_TILE / 4) + warp * (MC_ROWS * 32);  // first vector of this warp
-
-        uint4 q[MC_ROWS];
+    // A sub-tile's own 16-byte rows and the symbols just outside the warp's span (one before, up to
+    // three after), straight from global memory.  Loaded one sub-tile ahead: the next loads are
+    // issued as soon as the current sub-tile has been staged.
+    uint4 q[MC_ROWS];
+    uint32_t edge_prev = 0u, edge_n0 = 0u, edge_n1 = 0u, edge_n2 = 0u;
+    auto load_sub = [&](uint32_t vw) {  // vw = first vector of this warp's span
 #pragma unroll
         for (int j = 0; j < MC_ROWS; j++) {
-            const uint32_t v = vwarp + j * 32 + lane;
+            const uint32_t v = vw + j * 32 + lane;
             q[j] = (4u * v < N) ? src4[v] : make_uint4(0u, 0u, 0u, 0u);
         }
-        // the symbols just outside the warp's span come from global memory: one before, up to three after
-        uint32_t edge_prev = 0u, edge_n0 = 0u, edge_n1 = 0u, edge_n2 = 0u;
-        {
-            const uint32_t i0 = 4u * vwarp, i1 = 4u * (vwarp + MC_ROWS * 32);
-            if (lane == 0) edge_prev = (i0 > 0u && i0 - 1u < N) ? src[i0 - 1u] : 0u;
-            if (lane == 31) {
-                edge_n0 = (i1 < N) ? src[i1] : 0u;
-                if (INCR) {
-                    edge_n1 = (i1 + 1u < N) ? src[i1 + 1u] : 0u;
-                    edge_n2 = (i1 + 2u < N) ? src[i1 + 2u] : 0u;
-                }
-            }
-            if (LITERAL) {
-                // A symbol owned by another thread may already carry this merge's in-place rewrite;
-                // the new id is fresh, so mapping it back to `a` restores the snapshot.
-                if ((edge_prev & TOKEN_MASK) == NW) edge_prev = (edge_prev & WORD_START_BIT) | A;
-                if ((edge_n0 & TOKEN_MASK) == NW) edge_n0 = (edge_n0 & WORD_START_BIT) | A;
-                if ((edge_n1 & TOKEN_MASK) == NW) edge_n1 = (edge_n1 & WORD_START_BIT) | A;
-                if ((edge_n2 & TOKEN_MASK) == NW) edge_n2 = (edge_n2 & WORD_START_BIT) | A;
-            }
-        }
-        // row-crossing neighbours: lane 0 needs the previous row's lane 31, lane 31 the next row's lane 0
-        uint32_t last_w[MC_ROWS], first_x[MC_ROWS], first_y[MC_ROWS], first_z[MC_ROWS];
-#pragma unroll
-        for (int j = 0; j < MC_ROWS; j++) {
-            last_w[j] = __shfl_sync(0xFFFFFFFFu, q[j].w, 31);
-            first_x[j] = __shfl_sync(0xFFFFFFFFu, q[j].x, 0);
+        const uint32_t i0 = 4u * vw, i1 = 4u * (vw + MC_ROWS * 32);
+        edge_prev = edge_n0 = edge_n1 = edge_n2 = 0u;
+        if (lane == 0) edge_prev = (i0 > 0u && i0 - 1u < N) ? src[i0 - 1u] : 0u;
+        if (lane == 31) {
+            edge_n0 = (i1 < N) ? src[i1] : 0u;
             if (INCR) {
-                first_y[j] = __shfl_sync(0xFFFFFFFFu, q[j].y, 0);
-                first_z[j] = __shfl_sync(0xFFFFFFFFu, q[j].z, 0);
+                edge_n1 = (i1 + 1u < N) ? src[i1 + 1u] : 0u;
+                edge_n2 = (i1 + 2u < N) ? src[i1 + 2u] : 0u;
             }
         }
-        uint32_t keep = 0u;        // 4 bits per row
-        uint32_t rank[MC_ROWS];    // tile-local rank of this lane's first kept symbol of row j, within the warp
-        uint32_t run = 0u;         // kept symbols of the warp's earlier rows
-        // A warp whose whole span (and the three symbols after it) lies below both N and the
-        // compaction limit needs no bounds tests.
-        const bool interior = 4u * (vwarp + MC_ROWS * 32) + 3u < min(N, limit);  // incl. the look-ahead of the delta path
-#pragma unroll
-        for (int j = 0; j < MC_ROWS; j++) {
-            const uint32_t i0 = 4u * (vwarp + j * 32 + lane);
-            // s[0] = left neighbour, s[1..4] = own symbols, s[5] = right neighbour
-            uint32_t s[6];
-            s[0] = __shfl_up_sync(0xFFFFFFFFu, q[j].w, 1);
-            s[1] = q[j].x; s[2] = q[j].y; s[3] = q[j].z; s[4] = q[j].w;
-            s[5] = __shfl_down_sync(0xFFFFFFFFu, q[j].x, 1);
-            if (lane == 0) s[0] = j > 0 ? last_w[j > 0 ? j - 1 : 0] : edge_prev;
-            if (lane == 31) s[5] = j < MC_ROWS - 1 ? first_x[j < MC_ROWS - 1 ? j + 1 : j] : edge_n0;
-            // left[k]: s[k] is `a`; right[k]: s[k] is `b` and does not start a word.  A pair matches at
-            // k when left[k] & right[k + 1]; the symbol at k + 1 is then dropped (train.wgsl:482-497).
-            uint32_t left = 0u, right = 0u;
-#pragma unroll
-            for (int k = 0; k < 6; k++) {
-                left |= ((s[k] & TOKEN_MASK) == A ? 1u : 0u) << k;
-                right |= ((s[k] & (TOKEN_MASK | WORD_START_BIT)) == B ? 1u : 0u) << k;
-            }
-            uint32_t m = left & (right >> 1);   // bit k: pair (s[k], s[k+1]) merges, k = 0..4
-            uint32_t live = 0x3Fu;              // bit k: s[k] is a live position (bit 0: i0 >= 1; bit k >= 1: i0 + k - 1 < N)
-            if (!interior) {
-                live = (i0 >= 1u ? 1u : 0u);
-#pragma unroll
-                for (int k = 1; k < 6; k++) live |= (i0 + k - 1u < N ? 1u : 0u) << k;
-                m &= live & (live >> 1);
-            }
-            // own symbol t (t = 1..4): dropped iff m[t-1], rewritten iff m[t]
-            uint32_t kb = ~m & 15u;             // bit t-1 of kb ↔ own symbol t kept
-            const uint32_t rew = (m >> 1) & 15u;
-            if (!interior) {
-                uint32_t below = 0u;
-#pragma unroll
-                for (int k = 0; k < 4; k++) below |= (i0 + k < limit ? 1u : 0u) << k;
-                kb &= (live >> 1) & below;
-            }
-            if (INCR && deltas) {
-                // The pair (t, t+1) changes iff one of the pairs at t-1, t, t+1 merges.  For lanes 0..30
-                // those are matches some lane of this row sees in its own window; lane 31 also has to
-                // look at the two pairs that begin in the next row (or outside the warp's span).
-                uint32_t y = 0u, z = 0u;
-                bool far = false;
-                if (lane == 31) {
-                    y = j < MC_ROWS - 1 ? first_y[j < MC_ROWS - 1 ? j + 1 : j] : edge_n1;
-                    z = j < MC_ROWS - 1 ? first_z[j < MC_ROWS - 1 ? j + 1 : j] : edge_n2;
-                    const bool ly = interior || i0 + 5u < N, lz = interior || i0 + 6u < N;
-                    far = (ly && (s[5] & TOKEN_MASK) == A && (y & (TOKEN_MASK | WORD_START_BIT)) == B) ||
-                          (lz && (y & TOKEN_MASK) == A && (z & (TOKEN_MASK | WORD_START_BIT)) == B);
-                }
-                if (__any_sync(0xFFFFFFFFu, m != 0u || far))
-                    queue_deltas(st, table, dq, s[0], q[j], s[5], y, z, i0, N, interior, A, B, NW, lane, logC);
-            }
-            uint32_t ov[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                if ((rew >> k) & 1u) {
-                    ov[k] = NW | (ov[k] & WORD_START_BIT);
-                    if (LITERAL) src[i0 + k] = ov[k];  // the reference rewrites the source in place
-                }
-            }
-            q[j] = make_uint4(ov[0], ov[1], ov[2], ov[3]);
-            keep |= kb << (4 * j);
-            const uint32_t c = __popc(kb);
-            if (__all_sync(0xFFFFFFFFu, c == 4u)) {
-                rank[j] = run + 4u * lane;                   // nothing dropped in this row: ranks are positions
-                run += 128u;
-            } else {
-                uint32_t incl = c;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-                    if (lane >= o) incl += t;
-                }
-                rank[j] = run + incl - c;
-                run += __shfl_sync(0xFFFFFFFFu, incl, 31);
-            }
+        if (LITERAL) {
+            // A symbol owned by another thread may already carry this merge's in-place rewrite;
+            // the new id is fresh, so mapping it back to `a` restores the snapshot.
+            if ((edge_prev & TOKEN_MASK) == NW) edge_prev = (edge_prev & WORD_START_BIT) | A;
+            if ((edge_n0 & TOKEN_MASK) == NW) edge_n0 = (edge_n0 & WORD_START_BIT) | A;
+            if ((edge_n1 & TOKEN_MASK) == NW) edge_n1 = (edge_n1 & WORD_START_BIT) | A;
+            if ((edge_n2 & TOKEN_MASK) == NW) edge_n2 = (edge_n2 & WORD_START_BIT) | A;
         }
-        if (lane == 0) wsum[warp] = run;
-        __syncthreads();  // (B) warp totals visible; nobody reads s_tile after this point
+    };
+    auto span_of = [&](uint32_t tile, int sub) { return tile * (MC_TILE / 4) + sub * (MC_SUB / 4) + warp * (MC_ROWS * 32); };
 
-        // tile-local offset of this warp and the tile aggregate
-        uint32_t w = lane < MC_WARPS ? wsum[lane] : 0u;
-        uint32_t before = lane < warp ? w : 0u;
+    if (threadIdx.x == 0) s_tile = atomicAdd(&st->ticket, 1u);
+    __syncthreads();
+    uint32_t tile = s_tile;
+    if (tile < ntiles) load_sub(span_of(tile, 0));
+    while (tile < ntiles) {
+        if (threadIdx.x == 0) s_next = atomicAdd(&st->ticket, 1u);  // read after the first barrier below
+        uint32_t acc = 0u;  // kept symbols of the sub-tiles done so far (the same in every thread)
+        uint32_t next = 0u;
+#pragma unroll 1
+        for (int sub = 0; sub < MC_SUBS; sub++) {
+            const uint32_t vwarp = span_of(tile, sub);
+            uint32_t keep = 0u;        // 4 bits per row
+            uint32_t rank[MC_ROWS];    // rank of this lane's first kept symbol of row j within the warp's span
+            uint32_t run = 0u;         // kept symbols of the warp's earlier rows
+            // A warp whose whole span (and the three symbols after it) lies below both N and the
+            // compaction limit needs no bounds tests.
+            const bool interior = 4u * (vwarp + MC_ROWS * 32) + 3u < min(N, limit);
+            // Most rows hold no `a` at all, and a row can only be touched by this merge if it, the
+            // row before it (its lane 0 looks one symbol back) or the row after it (the delta path
+            // looks ahead) holds one.  A few votes find that out; untouched rows skip all matching.
+            uint32_t row_has_a = 0u;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            before += __shfl_xor_sync(0xFFFFFFFFu, before, o);
-            w += __shfl_xor_sync(0xFFFFFFFFu, w, o);
-        }
-        const uint32_t agg = w;
-        if (warp == 0 && lane == 0) {
-            const uint32_t flag = tile == 0u ? DESC_PREFIX : DESC_AGG;
-            st_desc(desc + tile, ((unsigned long long)((tag << 2) | flag) << 32) | agg);
-        }
-        // stage the kept symbols at their tile-local rank
+            for (int j = 0; j < MC_ROWS; j++) {
+                const bool has = (q[j].x & TOKEN_MASK) == A || (q[j].y & TOKEN_MASK) == A || (q[j].z & TOKEN_MASK) == A ||
+                                 (q[j].w & TOKEN_MASK) == A;
+                row_has_a |= (__any_sync(0xFFFFFFFFu, has) ? 1u : 0u) << (j + 1);
+            }
+            row_has_a |= __any_sync(0xFFFFFFFFu, lane == 0 && (edge_prev & TOKEN_MASK) == A) ? 1u : 0u;
+            if (INCR)
+                row_has_a |= (__any_sync(0xFFFFFFFFu, lane == 31 && ((edge_n0 & TOKEN_MASK) == A || (edge_n1 & TOKEN_MASK) == A)) ? 1u : 0u)
+                             << (MC_ROWS + 1);
 #pragma unroll
-        for (int j = 0; j < MC_ROWS; j++) {
-            uint32_t d = before + rank[j];
-            const uint32_t kb = (keep >> (4 * j)) & 15u;
-            if (kb & 1u) stage[d++] = q[j].x;
-            if (kb & 2u) stage[d++] = q[j].y;
-            if (kb & 4u) stage[d++] = q[j].z;
-            if (kb & 8u) stage[d++] = q[j].w;
+            for (int j = 0; j < MC_ROWS; j++) {
+                // bits j, j + 1, j + 2 of row_has_a: the row before (or the left edge), this row, the row after (or the right edge)
+                const uint32_t near_a = (row_has_a >> j) & (INCR ? 7u : 3u);
+                if (interior && near_a == 0u) {
+                    keep |= 15u << (4 * j);
+                    rank[j] = run + 4u * lane;
+                    run += 128u;
+                    continue;
+                }
+                const uint32_t i0 = 4u * (vwarp + j * 32 + lane);
+                // s[0] = left neighbour, s[1..4] = own symbols, s[5] = right neighbour.  Row-crossing
+                // neighbours come from the adjacent row's end lane; an earlier row may already hold
+                // this merge's rewritten values, and the fresh id maps back to `a`.
+                uint32_t s[6];
+                s[0] = __shfl_up_sync(0xFFFFFFFFu, q[j].w, 1);
+                s[1] = q[j].x; s[2] = q[j].y; s[3] = q[j].z; s[4] = q[j].w;
+                s[5] = __shfl_down_sync(0xFFFFFFFFu, q[j].x, 1);
+                {
+                    uint32_t pw = __shfl_sync(0xFFFFFFFFu, q[j > 0 ? j - 1 : 0].w, 31);
+                    if ((pw & TOKEN_MASK) == NW) pw = (pw & WORD_START_BIT) | A;
+                    const uint32_t nxr = __shfl_sync(0xFFFFFFFFu, q[j < MC_ROWS - 1 ? j + 1 : j].x, 0);
+                    if (lane == 0) s[0] = j > 0 ? pw : edge_prev;
+                    if (lane == 31) s[5] = j < MC_ROWS - 1 ? nxr : edge_n0;
+                }
+                // left[k]: s[k] is `a`; right[k]: s[k] is `b` and does not start a word.  A pair matches
+                // at k when left[k] & right[k + 1]; the symbol at k + 1 is then dropped (train.wgsl:482-497).
+                uint32_t left = 0u, right = 0u;
+#pragma unroll
+                for (int k = 0; k < 6; k++) {
+                    left |= ((s[k] & TOKEN_MASK) == A ? 1u : 0u) << k;
+                    right |= ((s[k] & (TOKEN_MASK | WORD_START_BIT)) == B ? 1u : 0u) << k;
+                }
+                uint32_t m = left & (right >> 1);   // bit k: pair (s[k], s[k+1]) merges, k = 0..4
+                uint32_t live = 0x3Fu;              // bit k: s[k] is a live position (bit 0: i0 >= 1; bit k >= 1: i0 + k - 1 < N)
+                if (!interior) {
+                    live = (i0 >= 1u ? 1u : 0u);
+#pragma unroll
+                    for (int k = 1; k < 6; k++) live |= (i0 + k - 1u < N ? 1u : 0u) << k;
+                    m &= live & (live >> 1);
+                }
+                // own symbol t (t = 1..4): dropped iff m[t-1], rewritten iff m[t]
+                uint32_t kb = ~m & 15u;             // bit t-1 of kb ↔ own symbol t kept
+                const uint32_t rew = (m >> 1) & 15u;
+                if (!interior) {
+                    uint32_t below = 0u;
+#pragma unroll
+                    for (int k = 0; k < 4; k++) below |= (i0 + k < limit ? 1u : 0u) << k;
+                    kb &= (live >> 1) & below;
+                }
+                if (INCR && deltas) {
+                    // The pair (t, t+1) changes iff one of the pairs at t-1, t, t+1 merges.  For lanes
+                    // 0..30 those are matches some lane of this row sees in its own window; lane 31 also
+                    // has to look at the two pairs that begin in the next row (or outside the span).
+                    const uint32_t ny = __shfl_sync(0xFFFFFFFFu, q[j < MC_ROWS - 1 ? j + 1 : j].y, 0);
+                    const uint32_t nz = __shfl_sync(0xFFFFFFFFu, q[j < MC_ROWS - 1 ? j + 1 : j].z, 0);
+                    uint32_t y = 0u, z = 0u;
+                    bool far = false;
+                    if (lane == 31) {
+                        y = j < MC_ROWS - 1 ? ny : edge_n1;
+                        z = j < MC_ROWS - 1 ? nz : edge_n2;
+                        const bool ly = interior || i0 + 5u < N, lz = interior || i0 + 6u < N;
+                        far = (ly && (s[5] & TOKEN_MASK) == A && (y & (TOKEN_MASK | WORD_START_BIT)) == B) ||
+                              (lz && (y & TOKEN_MASK) == A && (z & (TOKEN_MASK | WORD_START_BIT)) == B);
+                    }
+                    if (__any_sync(0xFFFFFFFFu, m != 0u || far))
+                        queue_deltas(st, table, dq, s[0], q[j], s[5], y, z, i0, N, interior, A, B, NW, lane, logC);
+                }
+                uint32_t ov[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    if ((rew >> k) & 1u) {
+                        ov[k] = NW | (ov[k] & WORD_START_BIT);
+                        if (LITERAL) src[i0 + k] = ov[k];  // the reference rewrites the source in place
+                    }
+                }
+                q[j] = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+                keep |= kb << (4 * j);
+                const uint32_t c = __popc(kb);
+                if (__all_sync(0xFFFFFFFFu, c == 4u)) {
+                    rank[j] = run + 4u * lane;               // nothing dropped in this row: ranks are positions
+                    run += 128u;
+                } else {
+                    uint32_t incl = c;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                        if (lane >= o) incl += t;
+                    }
+                    rank[j] = run + incl - c;
+                    run += __shfl_sync(0xFFFFFFFFu, incl, 31);
+                }
+            }
+            if (lane == 0) wsum[sub & 1][warp] = run;
+            __syncthreads();  // warp totals (and, in sub-tile 0, the next ticket) visible; wsum is double-buffered
+            if (sub == 0) next = s_next;
+            // offset of this warp within the sub-tile, and the sub-tile's kept count
+            uint32_t w = lane < MC_WARPS ? wsum[sub & 1][lane] : 0u;
+            uint32_t before = lane < warp ? w : 0u;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                before += __shfl_xor_sync(0xFFFFFFFFu, before, o);
+                w += __shfl_xor_sync(0xFFFFFFFFu, w, o);
+            }
+            before += acc;
+            // stage the kept symbols at their tile-local rank
+            if (run == MC_ROWS * 128u && (before & 3u) == 0u) {
+                // the whole warp kept everything: ranks are positions, whole 16-byte rows go out
+                uint4* __restrict__ st4 = reinterpret_cast<uint4*>(stage + before);
+#pragma unroll
+                for (int j = 0; j < MC_ROWS; j++) st4[j * 32 + lane] = q[j];
+            } else {
+#pragma unroll
+                for (int j = 0; j < MC_ROWS; j++) {
+                    uint32_t d = before + rank[j];
+                    const uint32_t kb = (keep >> (4 * j)) & 15u;
+                    if (kb & 1u) stage[d++] = q[j].x;
+                    if (kb & 2u) stage[d++] = q[j].y;
+                    if (kb & 4u) stage[d++] = q[j].z;
+                    if (kb & 8u) stage[d++] = q[j].w;
+                }
+            }
+            acc += w;
+            // the registers are free again: fetch the next sub-tile (of this tile or of the next one)
+            if (sub + 1 < MC_SUBS) load_sub(span_of(tile, sub + 1));
+            else if (next < ntiles) load_sub(span_of(next, 0));
         }
+        const uint32_t agg = acc;
         if (warp == 0) {
             uint32_t excl = 0u;
+            if (lane == 0) {
+                const uint32_t flag = tile == 0u ? DESC_PREFIX : DESC_AGG;
+                st_desc(desc + tile, ((unsigned long long)((tag << 2) | flag) << 32) | agg);
+            }
             if (tile != 0u) {
                 bool timed_out = false;
                 excl = lookback(desc, tile, tag, lane, &timed_out);
@@ -685,7 +744,6 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
             }
             if (lane == 0) {
                 s_base = excl;
-                s_agg = agg;
                 if (tile == ntiles - 1u) {
                     // Last tile: publish the new symbol count and advance the epoch.
                     const uint32_t total = excl + agg;
@@ -696,15 +754,23 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                     st->v_kept = total;
                     st->epoch = e + 1u;
                 }
-                s_tile = atomicAdd(&st->ticket, 1u);  // next tile; read after barrier (D)
             }
         }
-        __syncthreads();  // (C) staged run, base and next ticket visible
+        __syncthreads();  // staged run and its base visible
         {
-            const uint32_t base = s_base, cnt = s_agg;
-            for (uint32_t i = threadIdx.x; i < cnt; i += MC_THREADS) dst[base + i] = stage[i];
+            const uint32_t base = s_base;
+            if ((base & 3u) == 0u) {
+                // destination 16-byte aligned: vector stores, then the last few symbols one by one
+                const uint4* __restrict__ st4 = reinterpret_cast<const uint4*>(stage);
+                uint4* __restrict__ d4 = reinterpret_cast<uint4*>(dst + base);
+                for (uint32_t i = threadIdx.x; i < (agg >> 2); i += MC_THREADS) d4[i] = st4[i];
+                for (uint32_t i = (agg & ~3u) + threadIdx.x; i < agg; i += MC_THREADS) dst[base + i] = stage[i];
+            } else {
+                for (uint32_t i = threadIdx.x; i < agg; i += MC_THREADS) dst[base + i] = stage[i];
+            }
         }
-        __syncthreads();  // (D) stage and wsum may be reused
+        __syncthreads();  // the staging area may be reused
+        tile = next;
     }
     if (INCR && !deltas) {
         // a == b (or a rebuild is already due): no deltas were written, so nobody else touches the

@@ -92,6 +92,8 @@ typedef struct {
     /* launches of the count kernel that had nothing to do because the table was up to date */
     double pair_count_skipped_ms;
     uint64_t pair_count_skipped_launches;
+    /* the small kernels that fold the queued pair deltas (and the literal-mode tail) into the table */
+    double table_update_ms;
 } b200bpe_kernel_stats;
 
 const char* b200bpe_status_str(b200bpe_status);
