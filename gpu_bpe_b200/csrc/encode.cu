@@ -4,13 +4,13 @@
 // reference) and the host flow of TrieTokenizer.#encodeSinglePass (tokenizer.js:213-335).
 //
 // Device layout of the trie (built once per tokenizer from the v3 binary):
-//   * root_lut[256]   byte → packed child of the root, staged in shared memory by every CTA
+//   * nodes are renumbered: a node that ends a token gets the token id as its index, the others
+//     follow after the largest id, the root gets a reserved index
 //   * trans           open-addressing table (parent << 8 | byte) → packed child, 8 bytes per slot,
 //                     at most half full, pinned in L2 with an access-policy window
-//   * node_tok[]      node → token id, read once per emitted token
 // A packed child is  index | has_token << 31 | is_leaf << 30, so a step of the walk is one
-// table probe and needs no second load to learn whether the new node ends a token or has
-// children.  Each CTA also keeps a direct-mapped shared-memory cache of recent probes.
+// table probe and needs no second load to learn whether the new node ends a token (and which),
+// or whether it has children.  Each CTA keeps a direct-mapped shared-memory cache of recent probes.
 #include <algorithm>
 #include <cstring>
 #include <mutex>
@@ -23,30 +23,21 @@ namespace b200bpe {
 
 constexpr uint32_t T_MISS = 0xFFFFFFFFu;
 constexpr uint32_t T_EMPTY_KEY = 0xFFFFFFFFu;
-constexpr uint32_t T_HAS_TOKEN = 0x80000000u, T_LEAF = 0x40000000u, T_INDEX = 0x3FFFFFFFu;
+constexpr uint32_t T_HAS_TOKEN = 0x80000000u, T_LEAF = 0x40000000u, T_INDEX = 0x003FFFFFu;
+constexpr uint32_t T_ROOT = 0x003FFFFEu;   // index of the root in device numbering (no flags)
+constexpr uint32_t T_MAX_NODES = 0x003FFFF0u;
 
 constexpr int TW_THREADS = 512;
 constexpr int TW_CACHE_LOG2 = 13;  // 8192 entries * 8 B = 64 KB per CTA
+constexpr int TW_SMEM_BYTES = (1 << TW_CACHE_LOG2) * 8;
 constexpr int SC_THREADS = 256;    // scan/compaction: chunks per tile
 constexpr uint32_t SC_MAX_SPINS = 1u << 22;
 
 struct TrieDev {
-    const uint32_t* root_lut;
-    const uint2* trans;
+    const uint2* trans;      // {parent << 8 | byte, packed child}
     uint32_t trans_mask;
-    const uint32_t* node_tok;
 };
 
-__device__ __forceinline__ uint32_t hash_edge(uint32_t key) {
-    uint32_t x = key;
-    x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
-    return x;
-}
-static inline uint32_t hash_edge_host(uint32_t key) {
-    uint32_t x = key;
-    x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
-    return x;
-}
 
 // Where chunk g starts and ends.  Single buffer: fixed stride.  Batch: chunks are numbered
 // document by document (chunk_base = exclusive scan of per-document chunk counts) and never
@@ -68,74 +59,119 @@ __device__ __forceinline__ void chunk_span(uint64_t g, uint32_t cs, uint64_t n, 
     *hi = min(doc_off[a + 1], *lo + cs);
 }
 
-struct ByteWindow {
-    const uint4* base4;
-    uint64_t shift;   // misalignment of the byte pointer
-    uint64_t idx;
-    uint4 v;
-    __device__ __forceinline__ uint32_t get(uint64_t pos) {
-        const uint64_t ap = pos + shift;
-        const uint64_t i = ap >> 4;
-        if (i != idx) { v = __ldg(base4 + i); idx = i; }
-        const uint32_t w = (uint32_t)(ap >> 2) & 3u;
-        const uint32_t word = w == 0 ? v.x : w == 1 ? v.y : w == 2 ? v.z : v.w;
-        return (word >> (((uint32_t)ap & 3u) * 8u)) & 0xFFu;
-    }
-};
-
+// One thread walks one chunk.  The walk is a flat loop: every iteration either takes one
+// transition (one probe of the shared-memory cache, the root included) or ends the current token,
+// with the same instructions for every lane, so the lanes of a warp stay together although their
+// tokens end at different places.  Nodes that end a token are numbered by their token id, so the
+// packed child says which token ends there and ending a token costs no load.  Positions are
+// 32-bit offsets into the chunk; input is read one aligned 32-bit word at a time (the sector
+// stays in L1 for the next seven); tokens are buffered four at a time and stored as one 16-byte word.
 template <int THREADS, int CACHE_LOG2>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 3)
 k_trie_walk(TrieDev t, const uint8_t* __restrict__ bytes, uint64_t n, uint32_t cs, const uint64_t* __restrict__ doc_off,
             const uint64_t* __restrict__ chunk_base, uint32_t n_docs, uint64_t n_chunks_static,
-            uint32_t* __restrict__ staging, uint32_t* __restrict__ counts) {
+            uint32_t* __restrict__ staging, uint32_t* __restrict__ counts, uint32_t* __restrict__ ticket) {
     extern __shared__ __align__(16) unsigned char tw_smem[];
-    uint2* cache = reinterpret_cast<uint2*>(tw_smem);
-    uint32_t* lut = reinterpret_cast<uint32_t*>(cache + (1 << CACHE_LOG2));
+    uint2* cache = reinterpret_cast<uint2*>(tw_smem);  // {parent << 8 | byte, packed child}
     for (int i = threadIdx.x; i < (1 << CACHE_LOG2); i += THREADS) cache[i] = make_uint2(T_EMPTY_KEY, 0u);
-    for (int i = threadIdx.x; i < 256; i += THREADS) lut[i] = t.root_lut[i];
     __syncthreads();
     const uint64_t n_chunks = doc_off ? chunk_base[n_docs] : n_chunks_static;
-    ByteWindow win;
-    win.shift = reinterpret_cast<uintptr_t>(bytes) & 15u;
-    win.base4 = reinterpret_cast<const uint4*>(reinterpret_cast<uintptr_t>(bytes) - win.shift);
-    win.idx = ~0ull;
+    const uint32_t shift = (uint32_t)(reinterpret_cast<uintptr_t>(bytes) & 3u);
+    const uint32_t* __restrict__ words = reinterpret_cast<const uint32_t*>(reinterpret_cast<uintptr_t>(bytes) - shift);
+    const bool vec_ok = (cs & 3u) == 0u;  // chunk staging slots are 16-byte aligned
 
-    for (uint64_t g = (uint64_t)blockIdx.x * THREADS + threadIdx.x; g < n_chunks; g += (uint64_t)gridDim.x * THREADS) {
-        uint64_t pos, ce;
-        chunk_span(g, cs, n, doc_off, chunk_base, n_docs, &pos, &ce);
+    // Chunks are handed out 32 at a time to whichever warp is free (documents end in short chunks,
+    // so a fixed assignment would leave lanes and whole warps idle at the end).
+    const int lane = threadIdx.x & 31;
+    for (;;) {
+        uint32_t first = 0u;
+        if (lane == 0) first = atomicAdd(ticket, 32u);
+        first = __shfl_sync(0xFFFFFFFFu, first, 0);
+        if ((uint64_t)first >= n_chunks) break;
+        const uint64_t g = (uint64_t)first + lane;
+        if (g >= n_chunks) continue;
+        uint64_t lo, hi;
+        chunk_span(g, cs, n, doc_off, chunk_base, n_docs, &lo, &hi);
+        const uint32_t len = (uint32_t)(hi - lo);
+        const uint32_t* __restrict__ cw = words + ((lo + shift) >> 2);  // word holding the chunk's first byte
+        const uint32_t a0 = (uint32_t)((lo + shift) & 3u);              // and that byte's place in it
         uint32_t* __restrict__ out = staging + g * cs;
+        uint32_t widx = 0xFFFFFFFFu, word = 0u;
+        // bytes from the chunk's start to the end of the whole input: prefetches stay inside it
+        const uint32_t pf_limit = (uint32_t)min((unsigned long long)(n - lo), 0xFFFFFFFFull);
+        auto byte_at = [&](uint32_t r) -> uint32_t {
+            const uint32_t qq = a0 + r;
+            if ((qq >> 2) != widx) {
+                widx = qq >> 2;
+                word = __ldg(cw + widx);
+                // entering a new 32-byte sector: ask for the one after it now
+                if ((widx & 7u) == 0u && r + 72u < pf_limit) asm volatile("prefetch.global.L1 [%0];" ::"l"(cw + widx + 8));
+            }
+            return (word >> ((qq & 3u) * 8u)) & 0xFFu;
+        };
         uint32_t tw = 0;
-        while (pos < ce) {
-            const uint32_t first = win.get(pos);
-            uint32_t v = lut[first];
-            if (v == T_MISS) { out[tw++] = first; pos++; continue; }
-            uint64_t wp = pos + 1, lmp = pos;
-            uint32_t last = T_MISS;
-            if (v & T_HAS_TOKEN) { last = v & T_INDEX; lmp = wp; }
-            while (!(v & T_LEAF) && wp < ce) {
-                const uint32_t key = ((v & T_INDEX) << 8) | win.get(wp);
-                const uint32_t h = hash_edge(key);
-                const uint2 ce2 = cache[h & ((1 << CACHE_LOG2) - 1)];
-                uint32_t nv;
-                if (ce2.x == key) {
-                    nv = ce2.y;
+        uint4 buf = make_uint4(0u, 0u, 0u, 0u), buf_lo = make_uint4(0u, 0u, 0u, 0u);  // eight tokens = one 32-byte sector
+        uint32_t p = 0, w = 0, l = 0;   // token start, walk position, end of the longest token so far
+        uint32_t v = T_ROOT;            // packed current node
+        uint32_t last = 0u;
+        bool have = false;              // a token ends somewhere on the walk so far
+        while (p < len) {
+            uint32_t nv = T_MISS;
+            if (w < len && !(v & T_LEAF)) {
+                const uint32_t key = ((v & T_INDEX) << 8) | byte_at(w);
+                const uint32_t h = key * 0x9E3779B1u;
+                const uint32_t ci = h >> (32 - CACHE_LOG2);
+                const uint2 c = cache[ci];
+                if (c.x == key) {
+                    nv = c.y;
                 } else {
-                    uint32_t slot = (h >> 7) & t.trans_mask;
+                    uint32_t slot = (h ^ (h >> 15)) & t.trans_mask;
                     for (;;) {
                         const uint2 e = __ldg(t.trans + slot);
                         if (e.x == key) { nv = e.y; break; }
-                        if (e.x == T_EMPTY_KEY) { nv = T_MISS; break; }
+                        if (e.x == T_EMPTY_KEY) break;
                         slot = (slot + 1) & t.trans_mask;
                     }
-                    cache[h & ((1 << CACHE_LOG2) - 1)] = make_uint2(key, nv);
+                    cache[ci] = make_uint2(key, nv);  // misses are cached too
                 }
-                if (nv == T_MISS) break;
-                v = nv;
-                wp++;
-                if (v & T_HAS_TOKEN) { last = v & T_INDEX; lmp = wp; }
             }
-            if (last != T_MISS) { out[tw++] = __ldg(t.node_tok + last); pos = lmp; }
-            else { out[tw++] = first; pos++; }
+            if (nv != T_MISS) {
+                v = nv;
+                w++;
+                if (v & T_HAS_TOKEN) { have = true; last = v & T_INDEX; l = w; }
+            } else {
+                // the walk from p is over: emit the longest token seen, or the raw byte
+                const uint32_t tok = have ? last : byte_at(p);
+                p = have ? l : p + 1u;
+                const uint32_t k = tw & 3u;
+                buf.x = k == 0u ? tok : buf.x;
+                buf.y = k == 1u ? tok : buf.y;
+                buf.z = k == 2u ? tok : buf.z;
+                buf.w = k == 3u ? tok : buf.w;
+                if (k == 3u) {
+                    if ((tw & 4u) == 0u) {
+                        buf_lo = buf;  // first half of the sector: hold it back
+                    } else if (vec_ok) {
+                        uint4* __restrict__ o4 = reinterpret_cast<uint4*>(out + (tw & ~7u));
+                        o4[0] = buf_lo;
+                        o4[1] = buf;
+                    } else {
+                        uint32_t* __restrict__ o = out + (tw & ~7u);
+                        o[0] = buf_lo.x; o[1] = buf_lo.y; o[2] = buf_lo.z; o[3] = buf_lo.w;
+                        o[4] = buf.x; o[5] = buf.y; o[6] = buf.z; o[7] = buf.w;
+                    }
+                }
+                tw++;
+                w = p; v = T_ROOT; have = false;
+            }
+        }
+        {   // what is left of the last sector
+            uint32_t base = tw & ~7u;
+            if (tw & 4u) { out[base] = buf_lo.x; out[base + 1] = buf_lo.y; out[base + 2] = buf_lo.z; out[base + 3] = buf_lo.w; base += 4u; }
+            const uint32_t k = tw & 3u;
+            if (k > 0u) out[base] = buf.x;
+            if (k > 1u) out[base + 1] = buf.y;
+            if (k > 2u) out[base + 2] = buf.z;
         }
         counts[g] = tw;
     }
@@ -304,11 +340,9 @@ __global__ void k_doc_token_offsets(const uint64_t* __restrict__ chunk_base, con
 struct Tokenizer {
     Ctx* ctx = nullptr;
     uint32_t node_count = 0, edge_count = 0, max_token_len = 0, chunk = 0;
-    uint32_t* d_root_lut = nullptr;
     uint2* d_trans = nullptr;
     uint32_t trans_mask = 0;
     size_t trans_bytes = 0;
-    uint32_t* d_node_tok = nullptr;
     // pooled work buffers (grown on demand, as tokenizer.js:108-166 does)
     uint8_t* d_in = nullptr; uint64_t in_cap = 0;
     uint32_t* d_staging = nullptr; uint64_t staging_cap = 0;   // elements
@@ -327,7 +361,7 @@ struct Tokenizer {
 
     ~Tokenizer() {
         if (ctx) cudaSetDevice(ctx->device);
-        cudaFree(d_root_lut); cudaFree(d_trans); cudaFree(d_node_tok); cudaFree(d_in); cudaFree(d_staging);
+        cudaFree(d_trans); cudaFree(d_in); cudaFree(d_staging);
         cudaFree(d_counts); cudaFree(d_chunk_off); cudaFree(d_out); cudaFree(d_doc_off); cudaFree(d_chunk_base);
         cudaFree(d_tok_off); cudaFree(d_desc); cudaFree(d_ctl); cudaFree(d_total);
         if (h_total) cudaFreeHost(h_total);
@@ -370,19 +404,19 @@ struct Tokenizer {
         if (r) return r;
         const uint64_t ntiles = max_chunks / SC_THREADS + 2;
         B2_CUDA(cudaMemsetAsync(d_desc, 0, ntiles * 8, s));
-        B2_CUDA(cudaMemsetAsync(d_ctl, 0, 8, s));
+        B2_CUDA(cudaMemsetAsync(d_ctl, 0, 16, s));
         const uint64_t* cb = nullptr;
         if (d_docs) {
             if ((r = ensure(&d_chunk_base, &chunk_base_cap, (uint64_t)n_docs + 1))) return r;
             k_doc_chunk_scan<<<1, 1024, 0, s>>>(d_docs, n_docs, chunk, d_chunk_base);
             cb = d_chunk_base;
         }
-        TrieDev t{d_root_lut, d_trans, trans_mask, d_node_tok};
-        const size_t smem = (size_t)(1 << TW_CACHE_LOG2) * 8 + 1024;
+        TrieDev t{d_trans, trans_mask};
+        const size_t smem = TW_SMEM_BYTES;
         const int grid_w = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)ctx->sm_count * 3, (max_chunks + TW_THREADS - 1) / TW_THREADS));
         B2_CUDA(cudaEventRecord(ev[0], s));
         k_trie_walk<TW_THREADS, TW_CACHE_LOG2><<<grid_w, TW_THREADS, smem, s>>>(
-            t, d_bytes, n, chunk, d_docs, cb, n_docs, (n + chunk - 1) / chunk, d_staging, d_counts);
+            t, d_bytes, n, chunk, d_docs, cb, n_docs, (n + chunk - 1) / chunk, d_staging, d_counts, d_ctl + 2);
         B2_CUDA(cudaEventRecord(ev[1], s));
         const int grid_c = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)ctx->sm_count * 8, ntiles));
         k_scan_compact<<<grid_c, SC_THREADS, 0, s>>>(d_staging, d_counts, chunk, cb, n_docs, (n + chunk - 1) / chunk, d_desc,
@@ -423,7 +457,7 @@ b200bpe_status b200bpe_tokenizer_create(b200bpe_ctx* c, const void* trie, size_t
     b200bpe_status r = b200bpe_trie_parse_header(trie, len, f);
     if (r) return r;
     const uint32_t version = f[0], node_count = f[1], edge_count = f[2], max_len = f[3];
-    if (node_count == 0 || node_count > T_INDEX >> 8) return B200BPE_ERR_BAD_ARG;  // parent index must fit 22 bits + byte
+    if (node_count == 0 || node_count >= T_MAX_NODES) return B200BPE_ERR_BAD_ARG;  // a node index must fit 22 bits
     const uint8_t* base = static_cast<const uint8_t*>(trie) + 28;
     // unpack nodes / edges (v3: trie.js:209-249; v2 is the 16-bit legacy layout, parse-only in the reference)
     std::vector<uint32_t> nodes((size_t)node_count * 3), esym(edge_count), etgt(edge_count);
@@ -447,8 +481,35 @@ b200bpe_status b200bpe_tokenizer_create(b200bpe_ctx* c, const void* trie, size_t
             esym[e] = h[0] & 0xFF; etgt[e] = h[1];
         }
     }
+    // Device numbering: a node that ends a token is numbered by its token id, the others follow
+    // after the largest id; the root gets T_ROOT.
+    std::vector<uint32_t> dev_index(node_count, 0u);
+    {
+        uint32_t max_tok = 0;
+        for (uint32_t i = 0; i < node_count; i++) {
+            const uint32_t tk = nodes[(size_t)i * 3 + 2];
+            if (tk != INVALID_TOKEN) {
+                if (tk >= T_MAX_NODES) { set_last_error("token id too large for the device trie"); return B200BPE_ERR_BAD_ARG; }
+                max_tok = std::max(max_tok, tk);
+            }
+        }
+        std::vector<uint8_t> seen((size_t)max_tok + 1, 0);
+        uint32_t next_free = max_tok + 1;
+        for (uint32_t i = 0; i < node_count; i++) {
+            const uint32_t tk = nodes[(size_t)i * 3 + 2];
+            if (i == 0) { dev_index[i] = T_ROOT; continue; }  // the root ends no token the walk could emit
+            if (tk != INVALID_TOKEN) {
+                if (seen[tk]) { set_last_error("two trie nodes carry the same token id"); return B200BPE_ERR_BAD_ARG; }
+                seen[tk] = 1;
+                dev_index[i] = tk;
+            } else {
+                dev_index[i] = next_free++;
+            }
+        }
+        if (next_free >= T_MAX_NODES) { set_last_error("trie too large for the device layout"); return B200BPE_ERR_BAD_ARG; }
+    }
     auto packed = [&](uint32_t child) -> uint32_t {
-        uint32_t v = child;
+        uint32_t v = dev_index[child];
         if (nodes[(size_t)child * 3 + 2] != INVALID_TOKEN) v |= T_HAS_TOKEN;
         if ((nodes[(size_t)child * 3 + 1] & 0xFFFFu) == 0) v |= T_LEAF;
         return v;
@@ -456,16 +517,14 @@ b200bpe_status b200bpe_tokenizer_create(b200bpe_ctx* c, const void* trie, size_t
     uint32_t tlog = 4;
     while ((1ull << tlog) < (uint64_t)edge_count * 2 + 16) tlog++;
     std::vector<uint2> trans((size_t)1 << tlog, make_uint2(T_EMPTY_KEY, 0u));
-    std::vector<uint32_t> lut(256, T_MISS), ntok(node_count);
     const uint32_t tmask = (1u << tlog) - 1;
     for (uint32_t i = 0; i < node_count; i++) {
-        ntok[i] = nodes[(size_t)i * 3 + 2];
         const uint32_t fc = nodes[(size_t)i * 3], nc = nodes[(size_t)i * 3 + 1] & 0xFFFFu;  // tokenize.wgsl:102,115
         for (uint32_t e = fc; e < fc + nc; e++) {
-            if (e >= edge_count || etgt[e] >= node_count) return B200BPE_ERR_TRUNCATED_TRIE;
-            const uint32_t sym = esym[e] & 0xFFu, key = (i << 8) | sym;
-            if (i == 0) { if (lut[sym] == T_MISS) lut[sym] = packed(etgt[e]); continue; }
-            uint32_t slot = (hash_edge_host(key) >> 7) & tmask;
+            if (e >= edge_count || etgt[e] >= node_count || etgt[e] == 0) return B200BPE_ERR_TRUNCATED_TRIE;
+            const uint32_t sym = esym[e] & 0xFFu, key = (dev_index[i] << 8) | sym;
+            const uint32_t h = key * 0x9E3779B1u;
+            uint32_t slot = (h ^ (h >> 15)) & tmask;
             bool dup = false;
             while (trans[slot].x != T_EMPTY_KEY) {
                 if (trans[slot].x == key) { dup = true; break; }  // the binary search finds the first of equal symbols
@@ -483,18 +542,14 @@ b200bpe_status b200bpe_tokenizer_create(b200bpe_ctx* c, const void* trie, size_t
     cudaStream_t s = c->c.stream;
     auto fail = [&](b200bpe_status st) { delete t; return st; };
 #define B2_TRY(expr) if ((expr) != cudaSuccess) { set_last_error(std::string(#expr) + ": " + cudaGetErrorString(cudaGetLastError())); return fail(B200BPE_ERR_CUDA); }
-    B2_TRY(cudaMalloc(&t->d_root_lut, 1024));
     B2_TRY(cudaMalloc(&t->d_trans, trans.size() * 8));
-    B2_TRY(cudaMalloc(&t->d_node_tok, (size_t)node_count * 4));
-    B2_TRY(cudaMalloc(&t->d_ctl, 8));
+    B2_TRY(cudaMalloc(&t->d_ctl, 16));
     B2_TRY(cudaMalloc(&t->d_total, 8));
     B2_TRY(cudaMallocHost(&t->h_total, 16));
-    B2_TRY(cudaMemcpyAsync(t->d_root_lut, lut.data(), 1024, cudaMemcpyHostToDevice, s));
     B2_TRY(cudaMemcpyAsync(t->d_trans, trans.data(), trans.size() * 8, cudaMemcpyHostToDevice, s));
-    B2_TRY(cudaMemcpyAsync(t->d_node_tok, ntok.data(), (size_t)node_count * 4, cudaMemcpyHostToDevice, s));
     for (auto& e : t->ev) B2_TRY(cudaEventCreate(&e));
     B2_TRY(cudaFuncSetAttribute(k_trie_walk<TW_THREADS, TW_CACHE_LOG2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (1 << TW_CACHE_LOG2) * 8 + 1024));
+                                TW_SMEM_BYTES));
     t->trans_bytes = trans.size() * 8;
     B2_TRY(cudaStreamSynchronize(s));
 #undef B2_TRY
@@ -662,12 +717,12 @@ b200bpe_status b200bpe_encode_device_noalloc(b200bpe_tok* h, const uint8_t* d_by
     // the error flag must start at zero; everything else is written before it is read.
     const uint64_t ntiles = chunks / SC_THREADS + 2;
     B2_CUDA(cudaMemsetAsync(desc, 0, ntiles * 8, s));
-    B2_CUDA(cudaMemsetAsync(ctl, 0, 8, s));
-    TrieDev td{t->d_root_lut, t->d_trans, t->trans_mask, t->d_node_tok};
-    const size_t smem = (size_t)(1 << TW_CACHE_LOG2) * 8 + 1024;
+    B2_CUDA(cudaMemsetAsync(ctl, 0, 16, s));
+    TrieDev td{t->d_trans, t->trans_mask};
+    const size_t smem = TW_SMEM_BYTES;
     const int grid_w = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)t->ctx->sm_count * 3, (chunks + TW_THREADS - 1) / TW_THREADS));
     k_trie_walk<TW_THREADS, TW_CACHE_LOG2><<<grid_w, TW_THREADS, smem, s>>>(td, d_bytes, n, t->chunk, nullptr, nullptr, 0, chunks,
-                                                                       staging, counts);
+                                                                       staging, counts, ctl + 2);
     const int grid_c = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)t->ctx->sm_count * 8, ntiles));
     k_scan_compact<<<grid_c, SC_THREADS, 0, s>>>(staging, counts, t->chunk, nullptr, 0, chunks, desc, ctl, chunk_off,
                                                 d_tokens_out, cap, total);
