@@ -219,7 +219,7 @@ def main():
     ms_per_step = float(np.mean(step_ms))
     value = n_merges / (ms_per_step / 1e3)
     batches = (n_merges + 127) // 128
-    kernels_per_merge = (5 if mode == "literal" else 4) if world == 1 else 11
+    kernels_per_merge = (4 if mode == "literal" else 3) if world == 1 else 11
     gpu_launches = args.steps * (1 + batches * (1 + 128 * kernels_per_merge))
 
     # ── per-kernel device time: one more run with every kernel bracketed by CUDA events ──
@@ -239,7 +239,7 @@ def main():
     kern["pair_count"]["skipped_ms_total"] = ks["pair_count_skipped_ms"]
     kern["table_update"] = {"ms_total": ks["table_update_ms"], "launches": ks["merge_compact_launches"],
                             "avg_us": 1e3 * ks["table_update_ms"] / max(1, ks["merge_compact_launches"]),
-                            "what": "k_apply_deltas + k_literal_tail"}
+                            "what": "k_literal_tail (the queued pair deltas are folded in by k_merge_compact itself)"}
     if world > 1:
         kern["exchange"] = {"ms_total": ks["exchange_ms"], "launches": ks["exchange_launches"],
                             "avg_us": 1e3 * ks["exchange_ms"] / max(1, ks["exchange_launches"])}

@@ -56,6 +56,7 @@ struct DevState {
     uint32_t tail_fix;      // literal + incremental: the tail fix-up kernel has work for the merge just applied
     uint32_t fill_hwm;      // sharded runs: largest exchange-bucket fill seen on any rank since the batch began
     uint32_t pad[3];
+    PairSlot* table;        // the pair table (kept here so that replacing it does not invalidate a captured graph)
 };
 
 struct CtaBest {

@@ -70,6 +70,9 @@ struct Trainer {
     b200bpe_status build_graph();
     b200bpe_status enqueue_merge(int iter, bool timed);
     b200bpe_status grow_table();
+    // Kernel argument for the pair table: on one GPU the kernels take it from the control block, so a
+    // captured graph survives the table being replaced; the sharded path passes pointers.
+    PairSlot* ktable() const { return ctx->world > 1 ? table : nullptr; }
     b200bpe_status run(uint32_t max_merges, uint32_t* merges_out, uint32_t* counts_out, uint32_t* n_out,
                        uint32_t* early_out, b200bpe_progress_cb cb, void* user);
 };
@@ -94,7 +97,8 @@ b200bpe_status Trainer::alloc_common() {
     B2_CUDA(cudaMalloc(&buf[0], cap_elems * 4));
     B2_CUDA(cudaMalloc(&buf[1], cap_elems * 4));
     table_log2 = opts.table_log2;
-    if (table_log2 == 0) table_log2 = std::min<uint32_t>(21, std::max<uint32_t>(15, ceil_log2(n0 / 8 + 1)));
+    // Start small (every merge scans the whole table for the arg-max); it doubles when half full.
+    if (table_log2 == 0) table_log2 = std::min<uint32_t>(21, std::max<uint32_t>(15, ceil_log2(n0 / 128 + 1)));
     table_log2 = std::min(table_log2, MAX_TABLE_LOG2);
     B2_CUDA(cudaMalloc(&table, sizeof(PairSlot) << table_log2));
     B2_CUDA(cudaMalloc(&d_state, sizeof(DevState)));
@@ -164,6 +168,7 @@ b200bpe_status Trainer::init_state() {
     h_state->world = (uint32_t)ctx->world;
     h_state->incremental = incremental ? 1u : 0u;
     h_state->recount = 1u;
+    h_state->table = table;
     B2_CUDA(cudaMemcpyAsync(d_state, h_state, sizeof(DevState), cudaMemcpyHostToDevice, s));
     B2_CUDA(cudaEventRecord(ev_run1, s));
     B2_CUDA(cudaStreamSynchronize(s));
@@ -184,10 +189,11 @@ __global__ void k_begin_batch(DevState* st, uint32_t target) {
     st->merges_target = target;
     st->target_hit = (st->merges_done >= target) ? 1u : 0u;
 }
-__global__ void k_clear_status(DevState* st, uint32_t table_log2) {
+__global__ void k_clear_status(DevState* st, uint32_t table_log2, PairSlot* table) {
     st->status = DS_OK;
     st->want_grow = 0u;
     st->table_log2 = table_log2;
+    st->table = table;
     st->recount = 1u;  // the table is new and empty
 }
 
@@ -206,7 +212,7 @@ b200bpe_status Trainer::enqueue_merge(int iter, bool timed) {
         fflush(stderr);
     };
     B2_CUDA(ev(0));
-    k_pair_count<PC_SLOTS, PC_THREADS><<<grid_pc, PC_THREADS, PC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], table);
+    k_pair_count<PC_SLOTS, PC_THREADS><<<grid_pc, PC_THREADS, PC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], ktable());
     B2_CUDA(ev(1));
     dsync("pair_count");
     if (ctx->world > 1) {
@@ -215,20 +221,19 @@ b200bpe_status Trainer::enqueue_merge(int iter, bool timed) {
         B2_CUDA(ev(2));
     } else {
         B2_CUDA(ev(2));
-        k_argmax_setup<<<grid_am, AM_THREADS, 0, s>>>(d_state, table, d_cta_best, d_log, 0);
+        k_argmax_setup<<<grid_am, AM_THREADS, 0, s>>>(d_state, ktable(), d_cta_best, d_log, 0);
     }
     B2_CUDA(ev(3));
     dsync("argmax_setup");
     if (incremental) {
-        if (literal) k_merge_compact<true, true><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, table, dq);
-        else k_merge_compact<false, true><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, table, dq);
+        if (literal) k_merge_compact<true, true><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, ktable(), dq);
+        else k_merge_compact<false, true><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, ktable(), dq);
         B2_CUDA(ev(5));
-        k_apply_deltas<<<std::max(1, ctx->sm_count * 2), 256, 0, s>>>(d_state, dq, table);
-        if (literal) k_literal_tail<<<std::max(1, ctx->sm_count), 256, 0, s>>>(d_state, buf[0], buf[1], table);
+        if (literal) k_literal_tail<<<std::max(1, ctx->sm_count), 256, 0, s>>>(d_state, buf[0], buf[1], ktable());
     } else if (literal) {
-        k_merge_compact<true, false><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, table, dq);
+        k_merge_compact<true, false><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, ktable(), dq);
     } else {
-        k_merge_compact<false, false><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, table, dq);
+        k_merge_compact<false, false><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, ktable(), dq);
     }
     if (!incremental) B2_CUDA(ev(5));
     B2_CUDA(ev(4));
@@ -268,8 +273,8 @@ b200bpe_status Trainer::grow_table() {
         b200bpe_status r = xch.resize(ctx, table_log2);
         if (r) return r;
     }
-    k_clear_status<<<1, 1, 0, s>>>(d_state, table_log2);
-    if (graph) { cudaGraphExecDestroy(graph); graph = nullptr; }
+    k_clear_status<<<1, 1, 0, s>>>(d_state, table_log2, table);
+    if (graph && ctx->world > 1) { cudaGraphExecDestroy(graph); graph = nullptr; }
     return B200BPE_OK;
 }
 
@@ -360,7 +365,7 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
             if (over && xch.cap >= xch.cap_alloc) { h_state->status = DS_TABLE_FULL; }
             else if (xch.adapt(over, h_state->fill_hwm) || over) {
                 if (graph) { cudaGraphExecDestroy(graph); graph = nullptr; }
-                if (over) { k_clear_status<<<1, 1, 0, s>>>(d_state, table_log2); h_state->status = DS_OK; }
+                if (over) { k_clear_status<<<1, 1, 0, s>>>(d_state, table_log2, table); h_state->status = DS_OK; }
             }
         }
         if (h_state->status == DS_TABLE_FULL || h_state->want_grow) {
@@ -559,7 +564,7 @@ b200bpe_status b200bpe_trainer_pair_counts(b200bpe_trainer* h, uint64_t* keys_ou
         if (t->h_state->status == DS_BUCKET_FULL) {
             // No all-reduce on this path, so the ranks cannot agree on a larger bucket here: give up.
             cudaFree(dk); cudaFree(dc); cudaFree(dn);
-            k_clear_status<<<1, 1, 0, s>>>(t->d_state, t->table_log2);
+            k_clear_status<<<1, 1, 0, s>>>(t->d_state, t->table_log2, t->table);
             return B200BPE_ERR_CAPACITY;
         }
         const bool full = t->h_state->status == DS_TABLE_FULL;

@@ -98,7 +98,7 @@ __device__ __forceinline__ bool smem_count(uint32_t* __restrict__ skey, uint32_t
 template <int S, int THREADS>
 __global__ void __launch_bounds__(THREADS, PC_CTAS_PER_SM)
 k_pair_count(DevState* __restrict__ st, const uint32_t* __restrict__ buf0, const uint32_t* __restrict__ buf1,
-             PairSlot* __restrict__ table) {
+             PairSlot* table) {
     extern __shared__ __align__(16) unsigned char pc_smem[];
     uint32_t* skey = reinterpret_cast<uint32_t*>(pc_smem);
     uint32_t* scnt = skey + S;
@@ -107,13 +107,15 @@ k_pair_count(DevState* __restrict__ st, const uint32_t* __restrict__ buf0, const
     // runs (another CTA may find the table full), and a CTA must not split at a barrier.
     __shared__ uint32_t s_idle;
     if (threadIdx.x == 0) s_idle = st->early_stop | st->target_hit | st->status | (st->incremental & (st->recount ^ 1u));
-    for (int i = threadIdx.x; i < 2 * S; i += THREADS) skey[i] = 0u;
     __syncthreads();
     if (s_idle) return;
+    for (int i = threadIdx.x; i < 2 * S; i += THREADS) skey[i] = 0u;
+    __syncthreads();
     const uint32_t e = st->epoch;
     const uint32_t N = st->n[e & 1];
     const uint32_t* __restrict__ src = (e & 1) ? buf1 : buf0;
     const uint32_t logC = st->table_log2;
+    if (table == nullptr) table = st->table;
 
     const uint32_t nvec = (N + 3u) >> 2;
     uint32_t per = (nvec + gridDim.x - 1) / gridDim.x;
@@ -224,7 +226,7 @@ __device__ __forceinline__ void setup_merge(DevState* st, uint32_t best_count, u
 // mode 1: sharded — the last CTA only publishes this rank's best as a packed word for the
 //         all-reduce (count << 32 | ~pair32); k_unpack_flags finishes after the collective.
 __global__ void __launch_bounds__(AM_THREADS)
-k_argmax_setup(DevState* __restrict__ st, PairSlot* __restrict__ table, CtaBest* __restrict__ cta_best,
+k_argmax_setup(DevState* __restrict__ st, PairSlot* table, CtaBest* __restrict__ cta_best,
                uint32_t* __restrict__ log, int mode) {
     __shared__ uint32_t sc[AM_THREADS / 32];
     __shared__ unsigned long long sk[AM_THREADS / 32];
@@ -238,6 +240,7 @@ k_argmax_setup(DevState* __restrict__ st, PairSlot* __restrict__ table, CtaBest*
     }
     const uint32_t C = 1u << st->table_log2;
     const bool clear = st->incremental == 0u;  // an incrementally maintained table is never wiped here
+    if (table == nullptr) table = st->table;
     uint4* __restrict__ t4 = reinterpret_cast<uint4*>(table);
     uint32_t bc = 0, occ = 0;
     unsigned long long bk = 0ull;
@@ -365,8 +368,8 @@ __device__ __forceinline__ uint32_t lookback(const unsigned long long* __restric
 // Incremental table maintenance, the rare path of k_merge_compact: called by a whole warp for a row
 // in which some pair merges.  Every lane rebuilds an 8-symbol window (left neighbour, its four
 // symbols, the next three), finds which of its four (t, t+1) pairs change, and appends the old
-// pair to the "minus" queue and the new one to the "plus" queue; k_apply_deltas folds the queues
-// into the table afterwards.  With a != b matches never overlap, so the symbol after a dropped one
+// pair to the "minus" queue and the new one to the "plus" queue; the CTA folds its queues into the
+// table when it has run out of tiles.  With a != b matches never overlap, so the symbol after a dropped one
 // is always kept and this window is enough.  A full queue falls back to updating the table here.
 // Each CTA of the merge kernel appends to its own segment of the queues (segment g = CTA g), so the
 // reservation counters are never shared between CTAs.
@@ -463,39 +466,36 @@ __device__ __noinline__ void queue_deltas(DevState* st, PairSlot* __restrict__ t
     }
 }
 
-// Fold the delta queues of the merge just applied into the table, one CTA per segment at a time.
-// Equal keys held by the lanes of a warp are combined first (match-any), so a popular neighbour
-// pair costs one atomic per warp.  A segment's counters are cleared by the CTA that consumed it.
-__global__ void __launch_bounds__(256)
-k_apply_deltas(DevState* __restrict__ st, DeltaQueues dq, PairSlot* __restrict__ table) {
-    const uint32_t logC = st->table_log2;
+// Fold one queue segment into the table (the whole CTA takes part).  Equal keys held by the lanes
+// of a warp are combined first (match-any), so a popular neighbour pair costs one atomic per warp.
+// The segment's counters are cleared at the end.
+__device__ __forceinline__ void apply_segment(DevState* st, DeltaQueues dq, uint32_t g, PairSlot* __restrict__ table,
+                                              uint32_t logC) {
     const int lane = threadIdx.x & 31;
-    for (uint32_t g = blockIdx.x; g < dq.segments; g += gridDim.x) {
-        const uint32_t nm = min(dq.counts[2u * g], dq.seg_cap), np = min(dq.counts[2u * g + 1u], dq.seg_cap);
-        const uint32_t total = nm + np;
-        if (total == 0u) continue;
-        const uint32_t* __restrict__ seg_m = dq.minus + (size_t)g * dq.seg_cap;
-        const uint32_t* __restrict__ seg_p = dq.plus + (size_t)g * dq.seg_cap;
-        for (uint32_t base = 0; base < total; base += blockDim.x) {
-            const uint32_t i = base + threadIdx.x;
-            const bool on = i < total;
-            const bool neg = i < nm;
-            const uint32_t k32 = on ? (neg ? seg_m[i] : seg_p[i - nm]) : 0u;
-            // same key and same sign within the warp → one add of the group's size
-            const unsigned long long tagk = ((unsigned long long)(neg ? 1u : 0u) << 32) | k32;
-            const uint32_t act = __ballot_sync(0xFFFFFFFFu, on);
-            if (on) {
-                const uint32_t peers = __match_any_sync(act, tagk);
-                if (lane == __ffs(peers) - 1) {
-                    const unsigned long long key = ((unsigned long long)(k32 >> 16) << 32) | (k32 & 0xFFFFu);
-                    const uint32_t c = __popc(peers);
-                    table_add(table, logC, key, hash_pair(key), neg ? (0u - c) : c, st);
-                }
+    const uint32_t nm = min(dq.counts[2u * g], dq.seg_cap), np = min(dq.counts[2u * g + 1u], dq.seg_cap);
+    const uint32_t total = nm + np;
+    if (total == 0u) return;
+    const uint32_t* __restrict__ seg_m = dq.minus + (size_t)g * dq.seg_cap;
+    const uint32_t* __restrict__ seg_p = dq.plus + (size_t)g * dq.seg_cap;
+    for (uint32_t base = 0; base < total; base += blockDim.x) {
+        const uint32_t i = base + threadIdx.x;
+        const bool on = i < total;
+        const bool neg = i < nm;
+        const uint32_t k32 = on ? (neg ? seg_m[i] : seg_p[i - nm]) : 0u;
+        // same key and same sign within the warp → one add of the group's size
+        const unsigned long long tagk = ((unsigned long long)(neg ? 1u : 0u) << 32) | k32;
+        const uint32_t act = __ballot_sync(0xFFFFFFFFu, on);
+        if (on) {
+            const uint32_t peers = __match_any_sync(act, tagk);
+            if (lane == __ffs(peers) - 1) {
+                const unsigned long long key = ((unsigned long long)(k32 >> 16) << 32) | (k32 & 0xFFFFu);
+                const uint32_t c = __popc(peers);
+                table_add(table, logC, key, hash_pair(key), neg ? (0u - c) : c, st);
             }
         }
-        __syncthreads();
-        if (threadIdx.x == 0) { dq.counts[2u * g] = 0u; dq.counts[2u * g + 1u] = 0u; }
     }
+    __syncthreads();
+    if (threadIdx.x == 0) { dq.counts[2u * g] = 0u; dq.counts[2u * g + 1u] = 0u; }
 }
 
 // One tile = 16,384 symbols, worked through as four sub-tiles of 4,096: in a sub-tile warp w owns
@@ -519,7 +519,7 @@ k_apply_deltas(DevState* __restrict__ st, DeltaQueues dq, PairSlot* __restrict__
 template <bool LITERAL, bool INCR>
 __global__ void __launch_bounds__(MC_THREADS, 3)
 k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsigned long long* __restrict__ desc,
-                PairSlot* __restrict__ table, DeltaQueues dq) {
+                PairSlot* table, DeltaQueues dq) {
     extern __shared__ __align__(16) uint32_t stage[];  // MC_TILE words
     __shared__ uint32_t wsum[2][MC_WARPS];
     __shared__ uint32_t s_tile, s_next, s_base;
@@ -538,6 +538,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
     const uint4* src4 = reinterpret_cast<const uint4*>(src);
     const bool deltas = INCR && st->recount == 0u;
     const uint32_t logC = st->table_log2;
+    if (table == nullptr) table = st->table;
 
     // A sub-tile's own 16-byte rows and the symbols just outside the warp's span (one before, up to
     // three after), straight from global memory.  Loaded one sub-tile ahead: the next loads are
@@ -772,6 +773,13 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
         __syncthreads();  // the staging area may be reused
         tile = next;
     }
+    if (INCR && deltas) {
+        // Fold this CTA's queue segment into the table.  Nobody else reads or writes the segment,
+        // the updates commute with those of every other CTA, and doing it here, after the tiles,
+        // keeps the scattered table traffic out of the streaming loop without another launch.
+        __syncthreads();
+        apply_segment(st, dq, blockIdx.x, table, logC);
+    }
     if (INCR && !deltas) {
         // a == b (or a rebuild is already due): no deltas were written, so nobody else touches the
         // table during this launch; empty it for the full count that the next merge starts with.
@@ -789,9 +797,10 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
 // what the destination holds instead.  src = the merge's source buffer after its in-place
 // rewrites, dst = its destination; V = symbols copied, N1 = the new symbol count.
 __global__ void __launch_bounds__(256)
-k_literal_tail(DevState* __restrict__ st, const uint32_t* buf0, const uint32_t* buf1, PairSlot* __restrict__ table) {
+k_literal_tail(DevState* __restrict__ st, const uint32_t* buf0, const uint32_t* buf1, PairSlot* table) {
     // runs right after k_merge_compact of the same merge: k3_epoch is that merge, epoch already advanced
     if (!st->tail_fix) return;
+    if (table == nullptr) table = st->table;
     const uint32_t e = st->k3_epoch;
     const uint32_t N = st->n[e & 1], N1 = st->n[(e + 1u) & 1u], V = st->v_kept;
     const uint32_t* __restrict__ src = (e & 1) ? buf1 : buf0;
