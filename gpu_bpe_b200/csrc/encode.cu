@@ -115,55 +115,59 @@ k_trie_walk(TrieDev t, const uint8_t* __restrict__ bytes, uint64_t n, uint32_t c
         uint32_t v = T_ROOT;            // packed current node
         uint32_t last = 0u;
         bool have = false;              // a token ends somewhere on the walk so far
+        uint32_t fb = 0u;               // the byte at p, seen by the first step of every walk
+        // One iteration = one probe, then either a step or the end of a token; both outcomes are
+        // computed with selects so that all lanes run the same instructions.
         while (p < len) {
-            uint32_t nv = T_MISS;
-            if (w < len && !(v & T_LEAF)) {
-                const uint32_t key = ((v & T_INDEX) << 8) | byte_at(w);
-                const uint32_t h = key * 0x9E3779B1u;
-                const uint32_t ci = h >> (32 - CACHE_LOG2);
-                const uint2 c = cache[ci];
-                if (c.x == key) {
-                    nv = c.y;
+            const bool can = w < len && !(v & T_LEAF);
+            const uint32_t b = byte_at(min(w, len - 1u));
+            fb = (w == p) ? b : fb;
+            const uint32_t key = ((v & T_INDEX) << 8) | b;
+            const uint32_t h = key * 0x9E3779B1u;
+            const uint32_t ci = h >> (32 - CACHE_LOG2);
+            const uint2 c = cache[ci];
+            uint32_t nv = c.y;
+            if (c.x != key) {
+                nv = T_MISS;
+                uint32_t slot = (h ^ (h >> 15)) & t.trans_mask;
+                for (;;) {
+                    const uint2 e = __ldg(t.trans + slot);
+                    if (e.x == key) { nv = e.y; break; }
+                    if (e.x == T_EMPTY_KEY) break;
+                    slot = (slot + 1) & t.trans_mask;
+                }
+                cache[ci] = make_uint2(key, nv);  // misses are cached too
+            }
+            const bool step = can && nv != T_MISS;
+            const bool ends = step && (nv & T_HAS_TOKEN);
+            // the walk from p is over when there is no step: emit the longest token seen, or the raw byte
+            const uint32_t tok = have ? last : fb;
+            const uint32_t p_next = have ? l : p + 1u;
+            const uint32_t k = tw & 3u;
+            buf.x = (!step && k == 0u) ? tok : buf.x;
+            buf.y = (!step && k == 1u) ? tok : buf.y;
+            buf.z = (!step && k == 2u) ? tok : buf.z;
+            buf.w = (!step && k == 3u) ? tok : buf.w;
+            if (!step && k == 3u) {
+                if ((tw & 4u) == 0u) {
+                    buf_lo = buf;  // first half of the sector: hold it back
+                } else if (vec_ok) {
+                    uint4* __restrict__ o4 = reinterpret_cast<uint4*>(out + (tw & ~7u));
+                    o4[0] = buf_lo;
+                    o4[1] = buf;
                 } else {
-                    uint32_t slot = (h ^ (h >> 15)) & t.trans_mask;
-                    for (;;) {
-                        const uint2 e = __ldg(t.trans + slot);
-                        if (e.x == key) { nv = e.y; break; }
-                        if (e.x == T_EMPTY_KEY) break;
-                        slot = (slot + 1) & t.trans_mask;
-                    }
-                    cache[ci] = make_uint2(key, nv);  // misses are cached too
+                    uint32_t* __restrict__ o = out + (tw & ~7u);
+                    o[0] = buf_lo.x; o[1] = buf_lo.y; o[2] = buf_lo.z; o[3] = buf_lo.w;
+                    o[4] = buf.x; o[5] = buf.y; o[6] = buf.z; o[7] = buf.w;
                 }
             }
-            if (nv != T_MISS) {
-                v = nv;
-                w++;
-                if (v & T_HAS_TOKEN) { have = true; last = v & T_INDEX; l = w; }
-            } else {
-                // the walk from p is over: emit the longest token seen, or the raw byte
-                const uint32_t tok = have ? last : byte_at(p);
-                p = have ? l : p + 1u;
-                const uint32_t k = tw & 3u;
-                buf.x = k == 0u ? tok : buf.x;
-                buf.y = k == 1u ? tok : buf.y;
-                buf.z = k == 2u ? tok : buf.z;
-                buf.w = k == 3u ? tok : buf.w;
-                if (k == 3u) {
-                    if ((tw & 4u) == 0u) {
-                        buf_lo = buf;  // first half of the sector: hold it back
-                    } else if (vec_ok) {
-                        uint4* __restrict__ o4 = reinterpret_cast<uint4*>(out + (tw & ~7u));
-                        o4[0] = buf_lo;
-                        o4[1] = buf;
-                    } else {
-                        uint32_t* __restrict__ o = out + (tw & ~7u);
-                        o[0] = buf_lo.x; o[1] = buf_lo.y; o[2] = buf_lo.z; o[3] = buf_lo.w;
-                        o[4] = buf.x; o[5] = buf.y; o[6] = buf.z; o[7] = buf.w;
-                    }
-                }
-                tw++;
-                w = p; v = T_ROOT; have = false;
-            }
+            tw += step ? 0u : 1u;
+            p = step ? p : p_next;
+            w = step ? w + 1u : p_next;
+            last = ends ? (nv & T_INDEX) : last;
+            l = ends ? w : l;
+            have = step ? (have || ends) : false;
+            v = step ? nv : T_ROOT;
         }
         {   // what is left of the last sector
             uint32_t base = tw & ~7u;
