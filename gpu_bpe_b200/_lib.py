@@ -76,6 +76,7 @@ SIGNATURES = {
     "b200bpe_trie_parse_header": (C.c_int32, [C.c_void_p, C.c_size_t, u32p]),
     "b200bpe_tokenizer_create": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_uint32, C.POINTER(C.c_void_p)]),
     "b200bpe_tokenizer_info": (C.c_int32, [C.c_void_p, u32p, u32p, u32p, u32p]),
+    "b200bpe_tokenizer_layout": (C.c_int32, [C.c_void_p, u32p, u32p]),
     "b200bpe_encode": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64, u64p]),
     "b200bpe_encode_batch": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint64,
                                          C.c_void_p]),

@@ -5,12 +5,17 @@
 //
 // Device layout of the trie (built once per tokenizer from the v3 binary):
 //   * nodes are renumbered: a node that ends a token gets the token id as its index, the others
-//     follow after the largest id, the root gets a reserved index
-//   * trans           open-addressing table (parent << 8 | byte) → packed child, 8 bytes per slot,
-//                     at most half full, pinned in L2 with an access-policy window
-// A packed child is  index | has_token << 31 | is_leaf << 30, so a step of the walk is one
-// table probe and needs no second load to learn whether the new node ends a token (and which),
-// or whether it has children.  Each CTA keeps a direct-mapped shared-memory cache of recent probes.
+//     follow after the largest id, the root comes last (or gets a reserved index)
+//   * a packed child is  index | has_token | is_leaf, so a step of the walk is one lookup of
+//     (parent << 8 | byte) and needs no second load to learn whether the new node ends a token
+//     (and which), or whether it has children
+//   * small tries (every index below 2^16, a few ten thousand transitions): a cuckoo table of
+//     4-byte entries that every CTA copies into its shared memory.  The 24-bit key is permuted by
+//     an odd multiplier modulo 2^24; the top bits pick the slot and only the rest is stored next to
+//     the 18-bit packed child, so a lookup is two or three shared-memory loads and no branch
+//   * larger tries: an open-addressing table of 8-byte entries in global memory, at most half
+//     full, pinned in L2 with an access-policy window, behind a direct-mapped shared-memory cache
+//     of recent probes (hits and misses) per CTA
 #include <algorithm>
 #include <cstring>
 #include <mutex>
@@ -33,9 +38,18 @@ constexpr int TW_SMEM_BYTES = (1 << TW_CACHE_LOG2) * 8;
 constexpr int SC_THREADS = 256;    // scan/compaction: chunks per tile
 constexpr uint32_t SC_MAX_SPINS = 1u << 22;
 
+constexpr int CK_THREADS = 1024;   // cuckoo walk: one CTA per SM, the whole table in its shared memory
+constexpr uint32_t CK_MIN_LOG2 = 11, CK_MAX_LOG2 = 14;  // slots per sub-table
+constexpr uint32_t CK_HAS_TOKEN = 1u << 16, CK_LEAF = 1u << 17, CK_INDEX = 0xFFFFu, CK_VALUE = 0x3FFFFu;
+constexpr uint32_t CK_EMPTY = 0xFFFFFFFFu;
+
 struct TrieDev {
     const uint2* trans;      // {parent << 8 | byte, packed child}
     uint32_t trans_mask;
+    const uint32_t* cuckoo;  // D sub-tables of 1 << ck_log2 entries: remainder << 18 | packed child
+    uint32_t ck_log2;
+    uint32_t ck_mul[3];      // odd multipliers, one per sub-table
+    uint32_t root;           // packed root
 };
 
 
@@ -66,15 +80,27 @@ __device__ __forceinline__ void chunk_span(uint64_t g, uint32_t cs, uint64_t n, 
 // packed child says which token ends there and ending a token costs no load.  Positions are
 // 32-bit offsets into the chunk; input is read one aligned 32-bit word at a time (the sector
 // stays in L1 for the next seven); tokens are buffered four at a time and stored as one 16-byte word.
-template <int THREADS, int CACHE_LOG2>
-__global__ void __launch_bounds__(THREADS, 3)
+// D == 0: global table behind the probe cache.  D == 2 or 3: cuckoo table with D sub-tables in
+// shared memory (CACHE_LOG2 unused; the dynamic shared memory holds D << ck_log2 entries).
+template <int THREADS, int CACHE_LOG2, int D>
+__global__ void __launch_bounds__(THREADS, D == 0 ? 3 : 1)
 k_trie_walk(TrieDev t, const uint8_t* __restrict__ bytes, uint64_t n, uint32_t cs, const uint64_t* __restrict__ doc_off,
             const uint64_t* __restrict__ chunk_base, uint32_t n_docs, uint64_t n_chunks_static,
             uint32_t* __restrict__ staging, uint32_t* __restrict__ counts, uint32_t* __restrict__ ticket) {
     extern __shared__ __align__(16) unsigned char tw_smem[];
     uint2* cache = reinterpret_cast<uint2*>(tw_smem);  // {parent << 8 | byte, packed child}
-    for (int i = threadIdx.x; i < (1 << CACHE_LOG2); i += THREADS) cache[i] = make_uint2(T_EMPTY_KEY, 0u);
+    uint32_t* ck = reinterpret_cast<uint32_t*>(tw_smem);
+    constexpr uint32_t HAS = D == 0 ? T_HAS_TOKEN : CK_HAS_TOKEN, LEAF = D == 0 ? T_LEAF : CK_LEAF;
+    constexpr uint32_t INDEX = D == 0 ? T_INDEX : CK_INDEX;
+    if constexpr (D == 0) {
+        for (int i = threadIdx.x; i < (1 << CACHE_LOG2); i += THREADS) cache[i] = make_uint2(T_EMPTY_KEY, 0u);
+    } else {
+        const uint4* __restrict__ src = reinterpret_cast<const uint4*>(t.cuckoo);
+        for (uint32_t i = threadIdx.x; i < ((uint32_t)D << t.ck_log2) / 4u; i += THREADS)
+            reinterpret_cast<uint4*>(tw_smem)[i] = __ldg(src + i);
+    }
     __syncthreads();
+    const uint32_t ck_shift = 24u - t.ck_log2, ck_rmask = (1u << ck_shift) - 1u, ck_size = 1u << t.ck_log2;
     const uint64_t n_chunks = doc_off ? chunk_base[n_docs] : n_chunks_static;
     const uint32_t shift = (uint32_t)(reinterpret_cast<uintptr_t>(bytes) & 3u);
     const uint32_t* __restrict__ words = reinterpret_cast<const uint32_t*>(reinterpret_cast<uintptr_t>(bytes) - shift);
@@ -112,34 +138,45 @@ k_trie_walk(TrieDev t, const uint8_t* __restrict__ bytes, uint64_t n, uint32_t c
         uint32_t tw = 0;
         uint4 buf = make_uint4(0u, 0u, 0u, 0u), buf_lo = make_uint4(0u, 0u, 0u, 0u);  // eight tokens = one 32-byte sector
         uint32_t p = 0, w = 0, l = 0;   // token start, walk position, end of the longest token so far
-        uint32_t v = T_ROOT;            // packed current node
+        uint32_t v = t.root;            // packed current node
         uint32_t last = 0u;
         bool have = false;              // a token ends somewhere on the walk so far
         uint32_t fb = 0u;               // the byte at p, seen by the first step of every walk
         // One iteration = one probe, then either a step or the end of a token; both outcomes are
         // computed with selects so that all lanes run the same instructions.
         while (p < len) {
-            const bool can = w < len && !(v & T_LEAF);
+            const bool can = w < len && !(v & LEAF);
             const uint32_t b = byte_at(min(w, len - 1u));
             fb = (w == p) ? b : fb;
-            const uint32_t key = ((v & T_INDEX) << 8) | b;
-            const uint32_t h = key * 0x9E3779B1u;
-            const uint32_t ci = h >> (32 - CACHE_LOG2);
-            const uint2 c = cache[ci];
-            uint32_t nv = c.y;
-            if (c.x != key) {
-                nv = T_MISS;
-                uint32_t slot = (h ^ (h >> 15)) & t.trans_mask;
-                for (;;) {
-                    const uint2 e = __ldg(t.trans + slot);
-                    if (e.x == key) { nv = e.y; break; }
-                    if (e.x == T_EMPTY_KEY) break;
-                    slot = (slot + 1) & t.trans_mask;
+            const uint32_t key = ((v & INDEX) << 8) | b;
+            uint32_t nv;
+            if constexpr (D == 0) {
+                const uint32_t h = key * 0x9E3779B1u;
+                const uint32_t ci = h >> (32 - CACHE_LOG2);
+                const uint2 c = cache[ci];
+                nv = c.y;
+                if (c.x != key) {
+                    nv = T_MISS;
+                    uint32_t slot = (h ^ (h >> 15)) & t.trans_mask;
+                    for (;;) {
+                        const uint2 e = __ldg(t.trans + slot);
+                        if (e.x == key) { nv = e.y; break; }
+                        if (e.x == T_EMPTY_KEY) break;
+                        slot = (slot + 1) & t.trans_mask;
+                    }
+                    cache[ci] = make_uint2(key, nv);  // misses are cached too
                 }
-                cache[ci] = make_uint2(key, nv);  // misses are cached too
+            } else {
+                nv = T_MISS;
+#pragma unroll
+                for (int d = D - 1; d >= 0; d--) {
+                    const uint32_t h = (key * t.ck_mul[d]) & 0xFFFFFFu;
+                    const uint32_t e = ck[d * ck_size + (h >> ck_shift)];
+                    nv = (e >> 18) == (h & ck_rmask) ? (e & CK_VALUE) : nv;
+                }
             }
             const bool step = can && nv != T_MISS;
-            const bool ends = step && (nv & T_HAS_TOKEN);
+            const bool ends = step && (nv & HAS);
             // the walk from p is over when there is no step: emit the longest token seen, or the raw byte
             const uint32_t tok = have ? last : fb;
             const uint32_t p_next = have ? l : p + 1u;
@@ -164,10 +201,10 @@ k_trie_walk(TrieDev t, const uint8_t* __restrict__ bytes, uint64_t n, uint32_t c
             tw += step ? 0u : 1u;
             p = step ? p : p_next;
             w = step ? w + 1u : p_next;
-            last = ends ? (nv & T_INDEX) : last;
+            last = ends ? (nv & INDEX) : last;
             l = ends ? w : l;
             have = step ? (have || ends) : false;
-            v = step ? nv : T_ROOT;
+            v = step ? nv : t.root;
         }
         {   // what is left of the last sector
             uint32_t base = tw & ~7u;
@@ -344,9 +381,13 @@ __global__ void k_doc_token_offsets(const uint64_t* __restrict__ chunk_base, con
 struct Tokenizer {
     Ctx* ctx = nullptr;
     uint32_t node_count = 0, edge_count = 0, max_token_len = 0, chunk = 0;
-    uint2* d_trans = nullptr;
+    uint2* d_trans = nullptr;      // large tries: global transition table
     uint32_t trans_mask = 0;
     size_t trans_bytes = 0;
+    uint32_t* d_cuckoo = nullptr;  // small tries: cuckoo table, copied into shared memory by every CTA
+    int ck_d = 0;                  // its number of sub-tables (0: the global table is in use)
+    uint32_t ck_log2 = 0, ck_mul[3] = {1u, 1u, 1u};
+    uint32_t root = T_ROOT;
     // pooled work buffers (grown on demand, as tokenizer.js:108-166 does)
     uint8_t* d_in = nullptr; uint64_t in_cap = 0;
     uint32_t* d_staging = nullptr; uint64_t staging_cap = 0;   // elements
@@ -365,7 +406,7 @@ struct Tokenizer {
 
     ~Tokenizer() {
         if (ctx) cudaSetDevice(ctx->device);
-        cudaFree(d_trans); cudaFree(d_in); cudaFree(d_staging);
+        cudaFree(d_trans); cudaFree(d_cuckoo); cudaFree(d_in); cudaFree(d_staging);
         cudaFree(d_counts); cudaFree(d_chunk_off); cudaFree(d_out); cudaFree(d_doc_off); cudaFree(d_chunk_base);
         cudaFree(d_tok_off); cudaFree(d_desc); cudaFree(d_ctl); cudaFree(d_total);
         if (h_total) cudaFreeHost(h_total);
@@ -398,11 +439,34 @@ struct Tokenizer {
         return B200BPE_OK;
     }
 
+    size_t walk_smem() const { return ck_d == 0 ? (size_t)TW_SMEM_BYTES : ((size_t)ck_d << ck_log2) * 4; }
+
+    // The walk kernel for this tokenizer's trie layout; max_chunks only sizes the grid.
+    void walk(const uint8_t* d_bytes, uint64_t n, const uint64_t* d_docs, const uint64_t* cb, uint32_t n_docs,
+              uint64_t max_chunks, uint32_t* staging, uint32_t* counts, uint32_t* ticket) {
+        cudaStream_t s = ctx->stream;
+        TrieDev t{d_trans, trans_mask, d_cuckoo, ck_log2, {ck_mul[0], ck_mul[1], ck_mul[2]}, root};
+        const uint64_t n_static = (n + chunk - 1) / chunk;
+        if (ck_d == 0) {
+            const int grid = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)ctx->sm_count * 3, (max_chunks + TW_THREADS - 1) / TW_THREADS));
+            k_trie_walk<TW_THREADS, TW_CACHE_LOG2, 0><<<grid, TW_THREADS, walk_smem(), s>>>(
+                t, d_bytes, n, chunk, d_docs, cb, n_docs, n_static, staging, counts, ticket);
+        } else {
+            const int grid = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)ctx->sm_count, (max_chunks + CK_THREADS - 1) / CK_THREADS));
+            if (ck_d == 2)
+                k_trie_walk<CK_THREADS, 0, 2><<<grid, CK_THREADS, walk_smem(), s>>>(
+                    t, d_bytes, n, chunk, d_docs, cb, n_docs, n_static, staging, counts, ticket);
+            else
+                k_trie_walk<CK_THREADS, 0, 3><<<grid, CK_THREADS, walk_smem(), s>>>(
+                    t, d_bytes, n, chunk, d_docs, cb, n_docs, n_static, staging, counts, ticket);
+        }
+    }
+
     // Walk + scan/compact on device-resident inputs.  d_docs == nullptr → one buffer.
     b200bpe_status launch(const uint8_t* d_bytes, uint64_t n, const uint64_t* d_docs, uint32_t n_docs,
                           uint32_t* d_tokens, uint64_t cap, uint64_t* d_tok_offsets) {
         cudaStream_t s = ctx->stream;
-        set_persisting_window(ctx, d_trans, trans_bytes);  // keep the transition table resident in L2
+        if (ck_d == 0) set_persisting_window(ctx, d_trans, trans_bytes);  // keep the transition table resident in L2
         const uint64_t max_chunks = (n + chunk - 1) / chunk + (d_docs ? n_docs : 0);
         b200bpe_status r = ensure_work(std::max<uint64_t>(1, max_chunks));
         if (r) return r;
@@ -415,12 +479,8 @@ struct Tokenizer {
             k_doc_chunk_scan<<<1, 1024, 0, s>>>(d_docs, n_docs, chunk, d_chunk_base);
             cb = d_chunk_base;
         }
-        TrieDev t{d_trans, trans_mask};
-        const size_t smem = TW_SMEM_BYTES;
-        const int grid_w = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)ctx->sm_count * 3, (max_chunks + TW_THREADS - 1) / TW_THREADS));
         B2_CUDA(cudaEventRecord(ev[0], s));
-        k_trie_walk<TW_THREADS, TW_CACHE_LOG2><<<grid_w, TW_THREADS, smem, s>>>(
-            t, d_bytes, n, chunk, d_docs, cb, n_docs, (n + chunk - 1) / chunk, d_staging, d_counts, d_ctl + 2);
+        walk(d_bytes, n, d_docs, cb, n_docs, max_chunks, d_staging, d_counts, d_ctl + 2);
         B2_CUDA(cudaEventRecord(ev[1], s));
         const int grid_c = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)ctx->sm_count * 8, ntiles));
         k_scan_compact<<<grid_c, SC_THREADS, 0, s>>>(d_staging, d_counts, chunk, cb, n_docs, (n + chunk - 1) / chunk, d_desc,
@@ -486,22 +546,24 @@ b200bpe_status b200bpe_tokenizer_create(b200bpe_ctx* c, const void* trie, size_t
         }
     }
     // Device numbering: a node that ends a token is numbered by its token id, the others follow
-    // after the largest id; the root gets T_ROOT.
+    // after the largest id, the root comes last.
     std::vector<uint32_t> dev_index(node_count, 0u);
+    uint32_t root_index = 0;
     {
         uint32_t max_tok = 0;
-        for (uint32_t i = 0; i < node_count; i++) {
+        bool any = false;
+        for (uint32_t i = 1; i < node_count; i++) {
             const uint32_t tk = nodes[(size_t)i * 3 + 2];
             if (tk != INVALID_TOKEN) {
                 if (tk >= T_MAX_NODES) { set_last_error("token id too large for the device trie"); return B200BPE_ERR_BAD_ARG; }
                 max_tok = std::max(max_tok, tk);
+                any = true;
             }
         }
         std::vector<uint8_t> seen((size_t)max_tok + 1, 0);
-        uint32_t next_free = max_tok + 1;
-        for (uint32_t i = 0; i < node_count; i++) {
+        uint32_t next_free = any ? max_tok + 1 : 0;
+        for (uint32_t i = 1; i < node_count; i++) {
             const uint32_t tk = nodes[(size_t)i * 3 + 2];
-            if (i == 0) { dev_index[i] = T_ROOT; continue; }  // the root ends no token the walk could emit
             if (tk != INVALID_TOKEN) {
                 if (seen[tk]) { set_last_error("two trie nodes carry the same token id"); return B200BPE_ERR_BAD_ARG; }
                 seen[tk] = 1;
@@ -510,31 +572,103 @@ b200bpe_status b200bpe_tokenizer_create(b200bpe_ctx* c, const void* trie, size_t
                 dev_index[i] = next_free++;
             }
         }
-        if (next_free >= T_MAX_NODES) { set_last_error("trie too large for the device layout"); return B200BPE_ERR_BAD_ARG; }
+        root_index = next_free;  // the root ends no token the walk could emit
+        dev_index[0] = root_index;
+        if (root_index >= T_MAX_NODES) { set_last_error("trie too large for the device layout"); return B200BPE_ERR_BAD_ARG; }
     }
-    auto packed = [&](uint32_t child) -> uint32_t {
-        uint32_t v = dev_index[child];
-        if (nodes[(size_t)child * 3 + 2] != INVALID_TOKEN) v |= T_HAS_TOKEN;
-        if ((nodes[(size_t)child * 3 + 1] & 0xFFFFu) == 0) v |= T_LEAF;
-        return v;
-    };
-    uint32_t tlog = 4;
-    while ((1ull << tlog) < (uint64_t)edge_count * 2 + 16) tlog++;
-    std::vector<uint2> trans((size_t)1 << tlog, make_uint2(T_EMPTY_KEY, 0u));
-    const uint32_t tmask = (1u << tlog) - 1;
+    // the transitions, first of equal symbols only (the reference's binary search finds that one)
+    struct Transition { uint32_t key, child; };
+    std::vector<Transition> edges;
+    edges.reserve(edge_count);
     for (uint32_t i = 0; i < node_count; i++) {
         const uint32_t fc = nodes[(size_t)i * 3], nc = nodes[(size_t)i * 3 + 1] & 0xFFFFu;  // tokenize.wgsl:102,115
+        const size_t first = edges.size();
         for (uint32_t e = fc; e < fc + nc; e++) {
             if (e >= edge_count || etgt[e] >= node_count || etgt[e] == 0) return B200BPE_ERR_TRUNCATED_TRIE;
-            const uint32_t sym = esym[e] & 0xFFu, key = (dev_index[i] << 8) | sym;
-            const uint32_t h = key * 0x9E3779B1u;
-            uint32_t slot = (h ^ (h >> 15)) & tmask;
+            const uint32_t key = (dev_index[i] << 8) | (esym[e] & 0xFFu);
             bool dup = false;
-            while (trans[slot].x != T_EMPTY_KEY) {
-                if (trans[slot].x == key) { dup = true; break; }  // the binary search finds the first of equal symbols
-                slot = (slot + 1) & tmask;
+            for (size_t j = first; j < edges.size() && !dup; j++) dup = edges[j].key == key;
+            if (!dup) edges.push_back({key, etgt[e]});
+        }
+    }
+    auto is_token = [&](uint32_t node) { return nodes[(size_t)node * 3 + 2] != INVALID_TOKEN; };
+    auto is_leaf = [&](uint32_t node) { return (nodes[(size_t)node * 3 + 1] & 0xFFFFu) == 0; };
+
+    // Small tries: a cuckoo table for shared memory.  Try two sub-tables (at most 42 % full), then
+    // three (at most 80 % full); the environment variable B200BPE_TRIE_LAYOUT=hash forces the
+    // global table (for tests of that path).
+    std::vector<uint32_t> cuckoo;
+    int ck_d = 0;
+    uint32_t ck_log2 = 0, ck_mul[3] = {1u, 1u, 1u};
+    const char* layout = std::getenv("B200BPE_TRIE_LAYOUT");
+    const bool want_cuckoo = !(layout && std::strcmp(layout, "hash") == 0);
+    if (want_cuckoo && root_index <= CK_INDEX) {
+        uint64_t rng = 0x9E3779B97F4A7C15ull ^ ((uint64_t)edges.size() << 20);
+        auto next_rand = [&]() { rng ^= rng << 13; rng ^= rng >> 7; rng ^= rng << 17; return rng; };
+        for (int d = 2; d <= 3 && ck_d == 0; d++) {
+            const double max_load = d == 2 ? 0.42 : 0.80;
+            uint32_t k = CK_MIN_LOG2;
+            while (k <= CK_MAX_LOG2 && (double)edges.size() > max_load * (double)((uint64_t)d << k)) k++;
+            if (k > CK_MAX_LOG2) continue;
+            const uint32_t shift = 24u - k, rmask = (1u << shift) - 1u, size = 1u << k;
+            for (int attempt = 0; attempt < 64 && ck_d == 0; attempt++) {
+                uint32_t mul[3];
+                for (int j = 0; j < 3; j++) mul[j] = ((uint32_t)(next_rand() >> 20) | 1u) & 0xFFFFFFu;
+                std::vector<uint32_t> tab((size_t)d << k, CK_EMPTY), owner((size_t)d << k, 0u);  // owner: edge index
+                bool ok = true;
+                for (uint32_t e = 0; e < edges.size() && ok; e++) {
+                    uint32_t cur = e;
+                    int avoid = -1;
+                    ok = false;
+                    for (int kick = 0; kick < 512; kick++) {
+                        const uint32_t key = edges[cur].key;
+                        int placed = -1;
+                        for (int j = 0; j < d && placed < 0; j++) {
+                            const uint32_t h = (key * mul[j]) & 0xFFFFFFu;
+                            if (tab[(size_t)j * size + (h >> shift)] == CK_EMPTY) placed = j;
+                        }
+                        int j = placed;
+                        if (j < 0) {  // all candidate slots taken: evict one, not the one this key just left
+                            do { j = (int)(next_rand() % (uint64_t)d); } while (j == avoid);
+                        }
+                        const uint32_t h = (key * mul[j]) & 0xFFFFFFu;
+                        const size_t slot = (size_t)j * size + (h >> shift);
+                        uint32_t val = dev_index[edges[cur].child];
+                        if (is_token(edges[cur].child)) val |= CK_HAS_TOKEN;
+                        if (is_leaf(edges[cur].child)) val |= CK_LEAF;
+                        const uint32_t evicted = owner[slot];
+                        const bool was_empty = tab[slot] == CK_EMPTY;
+                        tab[slot] = ((h & rmask) << 18) | val;
+                        owner[slot] = cur;
+                        if (was_empty) { ok = true; break; }
+                        cur = evicted;
+                        avoid = j;
+                    }
+                }
+                if (ok) {
+                    cuckoo.swap(tab);
+                    ck_d = d; ck_log2 = k;
+                    for (int j = 0; j < 3; j++) ck_mul[j] = mul[j];
+                }
             }
-            if (!dup) trans[slot] = make_uint2(key, packed(etgt[e]));
+        }
+    }
+    // Larger tries (or on request): open addressing in global memory.
+    std::vector<uint2> trans;
+    uint32_t tmask = 0;
+    if (ck_d == 0) {
+        uint32_t tlog = 4;
+        while ((1ull << tlog) < (uint64_t)edges.size() * 2 + 16) tlog++;
+        trans.assign((size_t)1 << tlog, make_uint2(T_EMPTY_KEY, 0u));
+        tmask = (1u << tlog) - 1;
+        for (const Transition& e : edges) {
+            const uint32_t h = e.key * 0x9E3779B1u;
+            uint32_t slot = (h ^ (h >> 15)) & tmask;
+            while (trans[slot].x != T_EMPTY_KEY) slot = (slot + 1) & tmask;
+            uint32_t v = dev_index[e.child];
+            if (is_token(e.child)) v |= T_HAS_TOKEN;
+            if (is_leaf(e.child)) v |= T_LEAF;
+            trans[slot] = make_uint2(e.key, v);
         }
     }
     B2_CUDA(cudaSetDevice(c->c.device));
@@ -543,17 +677,32 @@ b200bpe_status b200bpe_tokenizer_create(b200bpe_ctx* c, const void* trie, size_t
     t->node_count = node_count; t->edge_count = edge_count; t->max_token_len = max_len;
     t->chunk = chunk_size ? chunk_size : std::max(512u, std::min(2048u, max_len * 8u));  // tokenizer.js:67-68
     t->trans_mask = tmask;
+    t->root = root_index;
+    t->ck_d = ck_d; t->ck_log2 = ck_log2;
+    for (int j = 0; j < 3; j++) t->ck_mul[j] = ck_mul[j];
     cudaStream_t s = c->c.stream;
     auto fail = [&](b200bpe_status st) { delete t; return st; };
 #define B2_TRY(expr) if ((expr) != cudaSuccess) { set_last_error(std::string(#expr) + ": " + cudaGetErrorString(cudaGetLastError())); return fail(B200BPE_ERR_CUDA); }
-    B2_TRY(cudaMalloc(&t->d_trans, trans.size() * 8));
+    if (ck_d == 0) {
+        B2_TRY(cudaMalloc(&t->d_trans, trans.size() * 8));
+        B2_TRY(cudaMemcpyAsync(t->d_trans, trans.data(), trans.size() * 8, cudaMemcpyHostToDevice, s));
+        B2_TRY(cudaFuncSetAttribute(k_trie_walk<TW_THREADS, TW_CACHE_LOG2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    TW_SMEM_BYTES));
+    } else {
+        B2_TRY(cudaMalloc(&t->d_cuckoo, cuckoo.size() * 4));
+        B2_TRY(cudaMemcpyAsync(t->d_cuckoo, cuckoo.data(), cuckoo.size() * 4, cudaMemcpyHostToDevice, s));
+        if (ck_d == 2) {
+            B2_TRY(cudaFuncSetAttribute(k_trie_walk<CK_THREADS, 0, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)(cuckoo.size() * 4)));
+        } else {
+            B2_TRY(cudaFuncSetAttribute(k_trie_walk<CK_THREADS, 0, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)(cuckoo.size() * 4)));
+        }
+    }
     B2_TRY(cudaMalloc(&t->d_ctl, 16));
     B2_TRY(cudaMalloc(&t->d_total, 8));
     B2_TRY(cudaMallocHost(&t->h_total, 16));
-    B2_TRY(cudaMemcpyAsync(t->d_trans, trans.data(), trans.size() * 8, cudaMemcpyHostToDevice, s));
     for (auto& e : t->ev) B2_TRY(cudaEventCreate(&e));
-    B2_TRY(cudaFuncSetAttribute(k_trie_walk<TW_THREADS, TW_CACHE_LOG2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                TW_SMEM_BYTES));
     t->trans_bytes = trans.size() * 8;
     B2_TRY(cudaStreamSynchronize(s));
 #undef B2_TRY
@@ -568,6 +717,18 @@ b200bpe_status b200bpe_tokenizer_info(b200bpe_tok* h, uint32_t* node_count, uint
     if (edge_count) *edge_count = h->t->edge_count;
     if (max_token_len) *max_token_len = h->t->max_token_len;
     if (chunk_size) *chunk_size = h->t->chunk;
+    return B200BPE_OK;
+}
+
+b200bpe_status b200bpe_tokenizer_layout(b200bpe_tok* h, uint32_t* sub_tables, uint32_t* log2_slots) {
+    if (!h) return B200BPE_ERR_BAD_ARG;
+    const Tokenizer* t = h->t;
+    if (sub_tables) *sub_tables = (uint32_t)t->ck_d;
+    if (log2_slots) {
+        uint32_t k = t->ck_log2;
+        if (t->ck_d == 0) for (k = 0; (1u << k) <= t->trans_mask; k++) {}
+        *log2_slots = k;
+    }
     return B200BPE_OK;
 }
 
@@ -722,11 +883,7 @@ b200bpe_status b200bpe_encode_device_noalloc(b200bpe_tok* h, const uint8_t* d_by
     const uint64_t ntiles = chunks / SC_THREADS + 2;
     B2_CUDA(cudaMemsetAsync(desc, 0, ntiles * 8, s));
     B2_CUDA(cudaMemsetAsync(ctl, 0, 16, s));
-    TrieDev td{t->d_trans, t->trans_mask};
-    const size_t smem = TW_SMEM_BYTES;
-    const int grid_w = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)t->ctx->sm_count * 3, (chunks + TW_THREADS - 1) / TW_THREADS));
-    k_trie_walk<TW_THREADS, TW_CACHE_LOG2><<<grid_w, TW_THREADS, smem, s>>>(td, d_bytes, n, t->chunk, nullptr, nullptr, 0, chunks,
-                                                                       staging, counts, ctl + 2);
+    t->walk(d_bytes, n, nullptr, nullptr, 0, chunks, staging, counts, ctl + 2);
     const int grid_c = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)t->ctx->sm_count * 8, ntiles));
     k_scan_compact<<<grid_c, SC_THREADS, 0, s>>>(staging, counts, t->chunk, nullptr, 0, chunks, desc, ctl, chunk_off,
                                                 d_tokens_out, cap, total);

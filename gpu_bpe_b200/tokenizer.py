@@ -35,6 +35,9 @@ class TrieTokenizer:
         cs = C.c_uint32()
         _lib.lib().b200bpe_tokenizer_info(h, None, None, None, C.byref(cs))
         self.chunkSize = cs.value
+        d, k = C.c_uint32(), C.c_uint32()
+        _lib.lib().b200bpe_tokenizer_layout(h, C.byref(d), C.byref(k))
+        self.deviceLayout = (d.value, k.value)   # (cuckoo sub-tables or 0, log2 of the slots per table)
 
     @staticmethod
     def fromVocab(engine, vocab, options: dict | None = None) -> "TrieTokenizer":

@@ -169,6 +169,10 @@ b200bpe_status b200bpe_tokenizer_create(b200bpe_ctx*, const void* trie_v3, size_
                                         b200bpe_tok** out);
 b200bpe_status b200bpe_tokenizer_info(b200bpe_tok*, uint32_t* node_count, uint32_t* edge_count,
                                       uint32_t* max_token_len, uint32_t* chunk_size);
+/* How the trie lies on the device (no reference counterpart; for diagnostics and tests):
+ * sub_tables 2 or 3 = cuckoo table held in shared memory, with 1 << log2_slots entries each;
+ * sub_tables 0 = open-addressing table in global memory with 1 << log2_slots entries. */
+b200bpe_status b200bpe_tokenizer_layout(b200bpe_tok*, uint32_t* sub_tables, uint32_t* log2_slots);
 /* encodeBytes (tokenizer.js:173-206): host bytes in, host token ids out.  cap is the room in
  * tokens_out (n is always enough).  The result depends only on (bytes, trie, chunk_size). */
 b200bpe_status b200bpe_encode(b200bpe_tok*, const uint8_t* bytes, uint64_t n, uint32_t* tokens_out, uint64_t cap,

@@ -10,6 +10,16 @@ from tests.helpers import small_text
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=["auto", "hash"])
+def trie_layout(request, monkeypatch):
+    """Every test runs on both device layouts of the trie: the one the library picks, and the global hash table forced."""
+    if request.param == "hash":
+        monkeypatch.setenv("B200BPE_TRIE_LAYOUT", "hash")
+    else:
+        monkeypatch.delenv("B200BPE_TRIE_LAYOUT", raising=False)
+    return request.param
+
+
 @pytest.fixture(scope="module")
 def trained():
     """A vocabulary trained by the oracle on config-2-shaped text (so the test does not depend on the GPU trainer)."""
@@ -19,9 +29,10 @@ def trained():
     return vocab, M.compile_vocab_to_trie(vocab)
 
 
-def test_tokenizer_fields_and_chunk_rule(engine, trained):
+def test_tokenizer_fields_and_chunk_rule(engine, trained, trie_layout):
     vocab, trie = trained
     tok = TrieTokenizer.fromVocab(engine, vocab)
+    assert (tok.deviceLayout[0] == 0) == (trie_layout == "hash")
     hdr = M.parse_trie(trie)
     assert (tok.nodeCount, tok.edgeCount, tok.maxTokenLen) == (hdr["nodeCount"], hdr["edgeCount"], hdr["maxTokenLen"])
     assert tok.chunkSize == max(512, min(2048, hdr["maxTokenLen"] * 8))
@@ -117,4 +128,24 @@ def test_train_then_encode_round_trip(engine):
     ids = tok.encodeBytes(data)
     assert tok.decode(ids) == data.tobytes() and ids.size < data.size // 2
     assert ids.tolist() == O.encode(data, compileVocabToTrie(res["vocab"]), tok.chunkSize, threads=4).tolist()
+    tok.destroy()
+
+
+@pytest.mark.parametrize("n_tokens,alphabet,want_tables", [(3_000, 64, 2), (14_000, 24, 3), (70_000, 256, 0)])
+def test_trie_sizes_pick_their_layout(engine, trie_layout, n_tokens, alphabet, want_tables):
+    """Random vocabularies sized for two cuckoo sub-tables, for three, and too large for shared memory."""
+    rng = np.random.default_rng(n_tokens)
+    vocab = [[b] for b in range(256)]
+    seen = set()
+    while len(vocab) < 256 + n_tokens:
+        t = tuple(int(x) for x in rng.integers(0, alphabet, int(rng.integers(2, 6))))
+        if t not in seen:
+            seen.add(t)
+            vocab.append(list(t))
+    trie = M.compile_vocab_to_trie(vocab)
+    tok = TrieTokenizer(engine, trie, vocab)
+    assert tok.deviceLayout[0] == (0 if trie_layout == "hash" else want_tables), tok.deviceLayout
+    data = rng.integers(0, alphabet, 400_000, dtype=np.uint8)
+    data[::97] = 255  # and bytes outside the alphabet
+    assert tok.encodeBytes(data).tolist() == O.encode(data, trie, tok.chunkSize, threads=4).tolist()
     tok.destroy()
