@@ -29,9 +29,10 @@ constexpr int MC_ROWS = 4;                               // uint4 rows per threa
 constexpr int MC_SUB = MC_THREADS * 4 * MC_ROWS;         // 4,096 symbols per sub-tile
 constexpr int MC_SUBS = 4;                               // sub-tiles per tile
 constexpr int MC_TILE = MC_SUB * MC_SUBS;                // 16,384 symbols per tile: one look-back each
-constexpr int MC_SMEM_BYTES = MC_TILE * 4;               // staging area (dynamic shared memory)
+constexpr int MC_SMEM_BYTES = (MC_TILE + 8) * 4;         // the tile and its edges (dynamic shared memory)
 constexpr int MC_WARPS = MC_THREADS / 32;
 constexpr uint32_t LOOKBACK_MAX_SPINS = 1u << 22;        // bounded wait; then DS_LOOKBACK_TIMEOUT
+constexpr uint32_t BULK_MAX_SPINS = 1u << 20;            // bounded wait for a bulk copy; then DS_LOOKBACK_TIMEOUT
 
 __device__ __forceinline__ uint32_t hash_pair(unsigned long long key) {
     uint32_t x = (uint32_t)key ^ ((uint32_t)(key >> 32) * 0x9E3779B1u);
@@ -498,17 +499,52 @@ __device__ __forceinline__ void apply_segment(DevState* st, DeltaQueues dq, uint
     if (threadIdx.x == 0) { dq.counts[2u * g] = 0u; dq.counts[2u * g + 1u] = 0u; }
 }
 
-// One tile = 16,384 symbols, worked through as four sub-tiles of 4,096: in a sub-tile warp w owns
-// the 512 consecutive symbols [w * 512, (w + 1) * 512) as four 16-byte rows per lane, so a warp's
-// kept symbols are contiguous in the output.  Per sub-tile: load, decide per symbol (rewritten?
-// dropped?), rank within the warp, and stage the kept symbols in shared memory right behind those
-// of the sub-tiles before it.  Per tile: publish the kept count, look back for the tile's global
-// offset (warp 0), copy the staged run out with coalesced stores.  Tiles are handed out by an
-// atomic ticket so that a waiting tile's predecessors are always running.
+// ── asynchronous bulk copy global → shared memory (one per tile), completion on an mbarrier ──
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, uint32_t arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(arrivals) : "memory");
+}
+// Orders this thread's earlier generic-proxy accesses to shared memory (and those ordered before
+// it by a barrier) before later writes by the asynchronous proxy.
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void bulk_load(void* dst_smem, const void* src, uint32_t bytes, unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst_smem)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait for the phase with the given parity; false when it never completed.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t spins = 0; spins < BULK_MAX_SPINS; spins++) {
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+// One tile = 16,384 symbols (64 KB).  One asynchronous bulk copy brings the whole tile into shared
+// memory; the tile is then worked through as four sub-tiles of 4,096 symbols: in a sub-tile warp w
+// owns the 512 consecutive symbols [w * 512, (w + 1) * 512) as four 16-byte rows per lane, so a
+// warp's kept symbols are contiguous in the output.  Per sub-tile: read the rows from shared
+// memory, decide per symbol (rewritten? dropped?), rank within the warp, barrier, and write the kept
+// symbols back into the SAME shared buffer at their tile-local rank (a rank never exceeds the
+// position it came from, and everything at or beyond the sub-tile's end is still untouched input).
+// Per tile: publish the kept count, look back for the tile's global offset (warp 0), copy the
+// compacted run out with 16-byte stores whatever the alignment of the destination, then start the
+// next tile's bulk copy.  Tiles are handed out by an atomic ticket so that a waiting tile's
+// predecessors are always running.
 //
-// Why four sub-tiles: the tiles of a launch move in waves, a wave resolves its offsets front to
-// back at one look-back window (32 tiles) per L2 round trip, and that chain, not HBM, bounds the
-// kernel when a tile is small.  One look-back per 64 KB of input moves the bound out of the way.
+// Why one look-back per 64 KB: the tiles of a launch move in waves, a wave resolves its offsets
+// front to back at one look-back window (32 tiles) per L2 round trip, and that chain, not HBM,
+// bounds the kernel when a tile is small.
+//
+// Neighbours across rows, sub-tiles and tiles are read from the shared buffer: the symbol before
+// the tile sits in front of it, the three after it behind it (plain loads).  Such a symbol may
+// already carry this merge's rewrite (in literal mode the source is rewritten in place by the
+// tile's owner; within the tile the last symbol of a sub-tile may have been written back onto
+// itself); the new id is fresh, so mapping it back to `a` restores the snapshot.
 //
 // INCR: the pair table is kept up to date instead of being rebuilt by a full count for the next
 // merge.  Every position whose pair with its right neighbour changes takes the old pair out and
@@ -516,13 +552,23 @@ __device__ __forceinline__ void apply_segment(DevState* st, DeltaQueues dq, uint
 // cannot overlap, so a dropped symbol's successor is always kept and three symbols of look-ahead
 // settle everything); a merge with a == b collapses whole runs (train.wgsl:482-497 on a run
 // "aaaa" yields one symbol), so it empties the table here and the next merge counts from scratch.
+#ifdef B200BPE_PHASES
+// Diagnostics build only: SM cycles that thread 0 of every CTA spent per phase of a tile.
+__device__ unsigned long long g_phase_cycles[8];
+#define PHASE_MARK(k) do { if (threadIdx.x == 0) { const long long t_ = clock64(); ph[k] += t_ - ph_last; ph_last = t_; } } while (0)
+#else
+#define PHASE_MARK(k) do {} while (0)
+#endif
+
 template <bool LITERAL, bool INCR>
 __global__ void __launch_bounds__(MC_THREADS, 3)
 k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsigned long long* __restrict__ desc,
                 PairSlot* table, DeltaQueues dq) {
-    extern __shared__ __align__(16) uint32_t stage[];  // MC_TILE words
-    __shared__ uint32_t wsum[2][MC_WARPS];
-    __shared__ uint32_t s_tile, s_next, s_base;
+    extern __shared__ __align__(16) uint32_t mc_smem[];  // 4 words (the last: left edge), the tile, 4 words (right edge)
+    uint32_t* const in = mc_smem + 4;
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ uint32_t wsum[2][MC_WARPS], wtot[MC_WARPS];
+    __shared__ uint32_t s_tile, s_next, s_base, s_fail;
     // `active`, `k3_epoch`, `n[k3_epoch & 1]`, `a`, `b`, `new_id`, `max_count` and `recount` are written
     // by the set-up step only, so every thread of every CTA of this launch reads the same values.
     if (!st->active) return;
@@ -535,170 +581,210 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
     const uint32_t ntiles = (N + MC_TILE - 1) / MC_TILE;
     const uint32_t tag = (e + 1u) & 0x3FFFFFFFu;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint4* src4 = reinterpret_cast<const uint4*>(src);
     const bool deltas = INCR && st->recount == 0u;
     const uint32_t logC = st->table_log2;
     if (table == nullptr) table = st->table;
+    auto snapshot = [&](uint32_t v) { return (v & TOKEN_MASK) == NW ? ((v & WORD_START_BIT) | A) : v; };
 
-    // A sub-tile's own 16-byte rows and the symbols just outside the warp's span (one before, up to
-    // three after), straight from global memory.  Loaded one sub-tile ahead: the next loads are
-    // issued as soon as the current sub-tile has been staged.
-    uint4 q[MC_ROWS];
-    uint32_t edge_prev = 0u, edge_n0 = 0u, edge_n1 = 0u, edge_n2 = 0u;
-    auto load_sub = [&](uint32_t vw) {  // vw = first vector of this warp's span
-#pragma unroll
-        for (int j = 0; j < MC_ROWS; j++) {
-            const uint32_t v = vw + j * 32 + lane;
-            q[j] = (4u * v < N) ? src4[v] : make_uint4(0u, 0u, 0u, 0u);
-        }
-        const uint32_t i0 = 4u * vw, i1 = 4u * (vw + MC_ROWS * 32);
-        edge_prev = edge_n0 = edge_n1 = edge_n2 = 0u;
-        if (lane == 0) edge_prev = (i0 > 0u && i0 - 1u < N) ? src[i0 - 1u] : 0u;
-        if (lane == 31) {
-            edge_n0 = (i1 < N) ? src[i1] : 0u;
-            if (INCR) {
-                edge_n1 = (i1 + 1u < N) ? src[i1 + 1u] : 0u;
-                edge_n2 = (i1 + 2u < N) ? src[i1 + 2u] : 0u;
-            }
-        }
-        if (LITERAL) {
-            // A symbol owned by another thread may already carry this merge's in-place rewrite;
-            // the new id is fresh, so mapping it back to `a` restores the snapshot.
-            if ((edge_prev & TOKEN_MASK) == NW) edge_prev = (edge_prev & WORD_START_BIT) | A;
-            if ((edge_n0 & TOKEN_MASK) == NW) edge_n0 = (edge_n0 & WORD_START_BIT) | A;
-            if ((edge_n1 & TOKEN_MASK) == NW) edge_n1 = (edge_n1 & WORD_START_BIT) | A;
-            if ((edge_n2 & TOKEN_MASK) == NW) edge_n2 = (edge_n2 & WORD_START_BIT) | A;
+    // Start the copy of a tile: thread 0 issues the bulk copy, threads 32..35 fetch the edges.
+    // Callers make sure (barrier) that nobody still reads the buffer.
+    auto fetch_tile = [&](uint32_t tile) {
+        const uint32_t i0 = tile * MC_TILE;
+        if (threadIdx.x == 0) {
+            const uint32_t bytes = ((min((uint32_t)MC_TILE, N - i0) + 3u) & ~3u) * 4u;
+            fence_proxy_async_smem();
+            bulk_load(in, src + i0, bytes, &bar);
+        } else if (threadIdx.x == 32) {
+            in[-1] = i0 > 0u ? src[i0 - 1u] : 0u;
+        } else if (threadIdx.x >= 33 && threadIdx.x < 36) {
+            const uint32_t k = threadIdx.x - 33u, i = i0 + MC_TILE + k;
+            in[MC_TILE + k] = i < N ? src[i] : 0u;
         }
     };
-    auto span_of = [&](uint32_t tile, int sub) { return tile * (MC_TILE / 4) + sub * (MC_SUB / 4) + warp * (MC_ROWS * 32); };
 
-    if (threadIdx.x == 0) s_tile = atomicAdd(&st->ticket, 1u);
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1u);
+        fence_proxy_async_smem();
+        s_fail = 0u;
+        s_tile = atomicAdd(&st->ticket, 1u);
+    }
     __syncthreads();
     uint32_t tile = s_tile;
-    if (tile < ntiles) load_sub(span_of(tile, 0));
+    uint32_t phase = 0u;
+#ifdef B200BPE_PHASES
+    long long ph[8] = {0, 0, 0, 0, 0, 0, 0, 0}, ph_last = clock64();
+#endif
+    if (tile < ntiles) fetch_tile(tile);
     while (tile < ntiles) {
-        if (threadIdx.x == 0) s_next = atomicAdd(&st->ticket, 1u);  // read after the first barrier below
-        uint32_t acc = 0u;  // kept symbols of the sub-tiles done so far (the same in every thread)
-        uint32_t next = 0u;
-#pragma unroll 1
+        if (threadIdx.x == 0) s_next = atomicAdd(&st->ticket, 1u);
+        PHASE_MARK(0);
+        if (!mbar_wait(&bar, phase)) s_fail = 1u;
+        phase ^= 1u;
+        __syncthreads();  // edges, next ticket and the failure flag visible
+        PHASE_MARK(1);
+        if (s_fail) {
+            if (threadIdx.x == 0) atomicExch(&st->status, (uint32_t)DS_LOOKBACK_TIMEOUT);
+            break;
+        }
+        const uint32_t next = s_next;
+        const uint32_t tile0 = tile * MC_TILE;  // first symbol of the tile
+
+        // ── pass 1: decide every symbol of the tile (kept? rewritten?) and count ──
+        // Straight-line code over the thread's sixteen rows; per row the decisions fit one byte
+        // (low nibble: own symbol kept, high nibble: own symbol rewritten), so they stay in four
+        // registers for pass 2.  The tile's kept count is published right after this pass, long
+        // before the tile needs its own offset, so the look-back chain runs under pass 2.
+        uint32_t dec[MC_SUBS];   // byte j = decisions of row j of the sub-tile
+        uint32_t far_bits = 0u;  // bit (4 * sub + j), lane 31 only: a pair merges just right of row j's right neighbour
+        uint32_t kept = 0u;
+#pragma unroll
         for (int sub = 0; sub < MC_SUBS; sub++) {
-            const uint32_t vwarp = span_of(tile, sub);
-            uint32_t keep = 0u;        // 4 bits per row
-            uint32_t rank[MC_ROWS];    // rank of this lane's first kept symbol of row j within the warp's span
-            uint32_t run = 0u;         // kept symbols of the warp's earlier rows
-            // A warp whose whole span (and the three symbols after it) lies below both N and the
-            // compaction limit needs no bounds tests.
-            const bool interior = 4u * (vwarp + MC_ROWS * 32) + 3u < min(N, limit);
-            // Most rows hold no `a` at all, and a row can only be touched by this merge if it, the
-            // row before it (its lane 0 looks one symbol back) or the row after it (the delta path
-            // looks ahead) holds one.  A few votes find that out; untouched rows skip all matching.
-            uint32_t row_has_a = 0u;
+            const uint32_t lw = sub * MC_SUB + warp * (MC_ROWS * 128);  // tile-local first symbol of the warp's span
+            const bool interior = tile0 + lw + MC_ROWS * 128u + 3u < min(N, limit);
+            uint32_t ab[MC_ROWS];  // bits 0..3: own symbol is `a`; bits 4..7: own symbol is `b` and does not start a word
 #pragma unroll
             for (int j = 0; j < MC_ROWS; j++) {
-                const bool has = (q[j].x & TOKEN_MASK) == A || (q[j].y & TOKEN_MASK) == A || (q[j].z & TOKEN_MASK) == A ||
-                                 (q[j].w & TOKEN_MASK) == A;
-                row_has_a |= (__any_sync(0xFFFFFFFFu, has) ? 1u : 0u) << (j + 1);
+                const uint4 q = reinterpret_cast<const uint4*>(in + lw)[j * 32 + lane];
+                ab[j] = ((q.x & TOKEN_MASK) == A ? 1u : 0u) | ((q.y & TOKEN_MASK) == A ? 2u : 0u) |
+                        ((q.z & TOKEN_MASK) == A ? 4u : 0u) | ((q.w & TOKEN_MASK) == A ? 8u : 0u) |
+                        ((q.x & (TOKEN_MASK | WORD_START_BIT)) == B ? 16u : 0u) | ((q.y & (TOKEN_MASK | WORD_START_BIT)) == B ? 32u : 0u) |
+                        ((q.z & (TOKEN_MASK | WORD_START_BIT)) == B ? 64u : 0u) | ((q.w & (TOKEN_MASK | WORD_START_BIT)) == B ? 128u : 0u);
             }
-            row_has_a |= __any_sync(0xFFFFFFFFu, lane == 0 && (edge_prev & TOKEN_MASK) == A) ? 1u : 0u;
-            if (INCR)
-                row_has_a |= (__any_sync(0xFFFFFFFFu, lane == 31 && ((edge_n0 & TOKEN_MASK) == A || (edge_n1 & TOKEN_MASK) == A)) ? 1u : 0u)
-                             << (MC_ROWS + 1);
+            // the symbol before the span (lane 0) and the three after it (lanes 1..3), as the same kind of bits
+            uint32_t edge = 0u;
+            if (lane < 4) {
+                const uint32_t v = snapshot(lane == 0 ? in[(int)lw - 1] : in[lw + MC_ROWS * 128u + (lane - 1)]);
+                edge = ((v & TOKEN_MASK) == A ? 1u : 0u) | ((v & (TOKEN_MASK | WORD_START_BIT)) == B ? 16u : 0u);
+            }
+            const uint32_t e_prev = __shfl_sync(0xFFFFFFFFu, edge, 0), e_n0 = __shfl_sync(0xFFFFFFFFu, edge, 1);
+            const uint32_t e_n1 = __shfl_sync(0xFFFFFFFFu, edge, 2), e_n2 = __shfl_sync(0xFFFFFFFFu, edge, 3);
+            uint32_t d = 0u;
 #pragma unroll
             for (int j = 0; j < MC_ROWS; j++) {
-                // bits j, j + 1, j + 2 of row_has_a: the row before (or the left edge), this row, the row after (or the right edge)
-                const uint32_t near_a = (row_has_a >> j) & (INCR ? 7u : 3u);
-                if (interior && near_a == 0u) {
-                    keep |= 15u << (4 * j);
-                    rank[j] = run + 4u * lane;
-                    run += 128u;
-                    continue;
-                }
-                const uint32_t i0 = 4u * (vwarp + j * 32 + lane);
-                // s[0] = left neighbour, s[1..4] = own symbols, s[5] = right neighbour.  Row-crossing
-                // neighbours come from the adjacent row's end lane; an earlier row may already hold
-                // this merge's rewritten values, and the fresh id maps back to `a`.
-                uint32_t s[6];
-                s[0] = __shfl_up_sync(0xFFFFFFFFu, q[j].w, 1);
-                s[1] = q[j].x; s[2] = q[j].y; s[3] = q[j].z; s[4] = q[j].w;
-                s[5] = __shfl_down_sync(0xFFFFFFFFu, q[j].x, 1);
-                {
-                    uint32_t pw = __shfl_sync(0xFFFFFFFFu, q[j > 0 ? j - 1 : 0].w, 31);
-                    if ((pw & TOKEN_MASK) == NW) pw = (pw & WORD_START_BIT) | A;
-                    const uint32_t nxr = __shfl_sync(0xFFFFFFFFu, q[j < MC_ROWS - 1 ? j + 1 : j].x, 0);
-                    if (lane == 0) s[0] = j > 0 ? pw : edge_prev;
-                    if (lane == 31) s[5] = j < MC_ROWS - 1 ? nxr : edge_n0;
-                }
-                // left[k]: s[k] is `a`; right[k]: s[k] is `b` and does not start a word.  A pair matches
-                // at k when left[k] & right[k + 1]; the symbol at k + 1 is then dropped (train.wgsl:482-497).
-                uint32_t left = 0u, right = 0u;
-#pragma unroll
-                for (int k = 0; k < 6; k++) {
-                    left |= ((s[k] & TOKEN_MASK) == A ? 1u : 0u) << k;
-                    right |= ((s[k] & (TOKEN_MASK | WORD_START_BIT)) == B ? 1u : 0u) << k;
-                }
-                uint32_t m = left & (right >> 1);   // bit k: pair (s[k], s[k+1]) merges, k = 0..4
-                uint32_t live = 0x3Fu;              // bit k: s[k] is a live position (bit 0: i0 >= 1; bit k >= 1: i0 + k - 1 < N)
-                if (!interior) {
-                    live = (i0 >= 1u ? 1u : 0u);
+                // left neighbour is `a`?  right neighbour is a mergeable `b`?
+                uint32_t pa = (__shfl_up_sync(0xFFFFFFFFu, ab[j], 1) >> 3) & 1u;
+                uint32_t nb = (__shfl_down_sync(0xFFFFFFFFu, ab[j], 1) >> 4) & 1u;
+                const uint32_t prev_row = j > 0 ? __shfl_sync(0xFFFFFFFFu, ab[j > 0 ? j - 1 : 0], 31) : 0u;
+                const uint32_t next_row = j < MC_ROWS - 1 ? __shfl_sync(0xFFFFFFFFu, ab[j < MC_ROWS - 1 ? j + 1 : j], 0) : 0u;
+                if (lane == 0) pa = j > 0 ? (prev_row >> 3) & 1u : e_prev & 1u;
+                if (lane == 31) nb = j < MC_ROWS - 1 ? (next_row >> 4) & 1u : (e_n0 >> 4) & 1u;
+                const uint32_t left = pa | ((ab[j] & 15u) << 1);          // bit k: s[k] is `a`, k = 0..4
+                const uint32_t right = (ab[j] >> 4) | (nb << 4);           // bit k: s[k + 1] is a mergeable `b`, k = 0..4
+                uint32_t m = left & right;                                 // bit k: pair (s[k], s[k+1]) merges
+                uint32_t kb, rew;
+                if (interior) {
+                    kb = ~m & 15u;             // own symbol t (t = 1..4) is dropped iff m[t-1]
+                    rew = (m >> 1) & 15u;      // and rewritten iff m[t]
+                } else {
+                    const uint32_t i0 = tile0 + lw + 4u * (j * 32 + lane);
+                    uint32_t live = (i0 >= 1u ? 1u : 0u), below = 0u;  // live bit k: s[k] exists (bit 0: i0 >= 1; bit k: i0 + k - 1 < N)
 #pragma unroll
                     for (int k = 1; k < 6; k++) live |= (i0 + k - 1u < N ? 1u : 0u) << k;
-                    m &= live & (live >> 1);
-                }
-                // own symbol t (t = 1..4): dropped iff m[t-1], rewritten iff m[t]
-                uint32_t kb = ~m & 15u;             // bit t-1 of kb ↔ own symbol t kept
-                const uint32_t rew = (m >> 1) & 15u;
-                if (!interior) {
-                    uint32_t below = 0u;
 #pragma unroll
                     for (int k = 0; k < 4; k++) below |= (i0 + k < limit ? 1u : 0u) << k;
-                    kb &= (live >> 1) & below;
+                    m &= live & (live >> 1);
+                    kb = ~m & 15u & (live >> 1) & below;
+                    rew = (m >> 1) & 15u;
                 }
-                if (INCR && deltas) {
-                    // The pair (t, t+1) changes iff one of the pairs at t-1, t, t+1 merges.  For lanes
-                    // 0..30 those are matches some lane of this row sees in its own window; lane 31 also
-                    // has to look at the two pairs that begin in the next row (or outside the span).
-                    const uint32_t ny = __shfl_sync(0xFFFFFFFFu, q[j < MC_ROWS - 1 ? j + 1 : j].y, 0);
-                    const uint32_t nz = __shfl_sync(0xFFFFFFFFu, q[j < MC_ROWS - 1 ? j + 1 : j].z, 0);
-                    uint32_t y = 0u, z = 0u;
-                    bool far = false;
-                    if (lane == 31) {
-                        y = j < MC_ROWS - 1 ? ny : edge_n1;
-                        z = j < MC_ROWS - 1 ? nz : edge_n2;
-                        const bool ly = interior || i0 + 5u < N, lz = interior || i0 + 6u < N;
-                        far = (ly && (s[5] & TOKEN_MASK) == A && (y & (TOKEN_MASK | WORD_START_BIT)) == B) ||
-                              (lz && (y & TOKEN_MASK) == A && (z & (TOKEN_MASK | WORD_START_BIT)) == B);
+                d |= (kb | (rew << 4)) << (8 * j);
+                kept += __popc(kb);
+                if (INCR) {
+                    // lane 31: do the pairs (s[5], y) or (y, z) merge, y and z being the two symbols after s[5]?
+                    // Those are the next row's first three symbols, or the span's right edge.
+                    bool far;
+                    if (j < MC_ROWS - 1) far = ((next_row & 1u) && (next_row & 32u)) || ((next_row & 2u) && (next_row & 64u));
+                    else far = ((e_n0 & 1u) && (e_n1 & 16u)) || ((e_n1 & 1u) && (e_n2 & 16u));
+                    if (!interior) {
+                        const uint32_t i0 = tile0 + lw + 4u * (j * 32 + 31);
+                        if (j < MC_ROWS - 1) far = ((next_row & 1u) && (next_row & 32u) && i0 + 5u < N) || ((next_row & 2u) && (next_row & 64u) && i0 + 6u < N);
+                        else far = ((e_n0 & 1u) && (e_n1 & 16u) && i0 + 5u < N) || ((e_n1 & 1u) && (e_n2 & 16u) && i0 + 6u < N);
                     }
-                    if (__any_sync(0xFFFFFFFFu, m != 0u || far))
-                        queue_deltas(st, table, dq, s[0], q[j], s[5], y, z, i0, N, interior, A, B, NW, lane, logC);
+                    if (lane == 31 && far) far_bits |= 1u << (4 * sub + j);
                 }
-                uint32_t ov[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
+            }
+            dec[sub] = d;
+        }
+        {
+            // the tile's kept count: warp sums, one barrier, everybody adds the eight sums
+            uint32_t ws = kept;
 #pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    if ((rew >> k) & 1u) {
-                        ov[k] = NW | (ov[k] & WORD_START_BIT);
-                        if (LITERAL) src[i0 + k] = ov[k];  // the reference rewrites the source in place
-                    }
-                }
-                q[j] = make_uint4(ov[0], ov[1], ov[2], ov[3]);
-                keep |= kb << (4 * j);
-                const uint32_t c = __popc(kb);
-                if (__all_sync(0xFFFFFFFFu, c == 4u)) {
-                    rank[j] = run + 4u * lane;               // nothing dropped in this row: ranks are positions
-                    run += 128u;
-                } else {
-                    uint32_t incl = c;
+            for (int o = 16; o > 0; o >>= 1) ws += __shfl_xor_sync(0xFFFFFFFFu, ws, o);
+            if (lane == 0) wtot[warp] = ws;
+        }
+        __syncthreads();
+        uint32_t agg = 0u;
 #pragma unroll
-                    for (int o = 1; o < 32; o <<= 1) {
-                        const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-                        if (lane >= o) incl += t;
+        for (int w = 0; w < MC_WARPS; w++) agg += wtot[w];
+        if (threadIdx.x == 0) {
+            const uint32_t flag = tile == 0u ? DESC_PREFIX : DESC_AGG;
+            st_desc(desc + tile, ((unsigned long long)((tag << 2) | flag) << 32) | agg);
+        }
+        PHASE_MARK(2);
+
+        // ── pass 2: rank the kept symbols and write them back at their tile-local rank ──
+        uint32_t acc = 0u;  // kept symbols of the sub-tiles done so far (the same in every thread)
+#pragma unroll 1
+        for (int sub = 0; sub < MC_SUBS; sub++) {
+            const uint32_t lw = sub * MC_SUB + warp * (MC_ROWS * 128);
+            const uint32_t d = sub == 0 ? dec[0] : sub == 1 ? dec[1] : sub == 2 ? dec[2] : dec[3];
+            uint4 q[MC_ROWS];
+#pragma unroll
+            for (int j = 0; j < MC_ROWS; j++) q[j] = reinterpret_cast<const uint4*>(in + lw)[j * 32 + lane];
+            uint32_t rank[MC_ROWS];    // rank of this lane's first kept symbol of row j within the warp's span
+            uint32_t run = MC_ROWS * 128u;
+            const uint32_t far4 = INCR ? (far_bits >> (4 * sub)) & 15u : 0u;
+            // nothing of the warp's span dropped or rewritten (and no delta to queue): ranks are positions
+            const bool untouched = __all_sync(0xFFFFFFFFu, d == 0x0F0F0F0Fu && far4 == 0u);
+            if (!untouched) {
+                // kept counts of the four rows as four byte lanes of one word (a row keeps at most 128, so no lane overflows)
+                uint32_t cnt = 0u;
+#pragma unroll
+                for (int j = 0; j < MC_ROWS; j++) cnt |= (uint32_t)__popc((d >> (8 * j)) & 15u) << (8 * j);
+                uint32_t incl = cnt;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                    if (lane >= o) incl += t;
+                }
+                const uint32_t tot = __shfl_sync(0xFFFFFFFFu, incl, 31);
+                run = 0u;
+#pragma unroll
+                for (int j = 0; j < MC_ROWS; j++) {
+                    rank[j] = run + ((incl >> (8 * j)) & 0xFFu) - ((cnt >> (8 * j)) & 0xFFu);
+                    run += (tot >> (8 * j)) & 0xFFu;
+                }
+#pragma unroll
+                for (int j = 0; j < MC_ROWS; j++) {
+                    const uint32_t rew = (d >> (8 * j + 4)) & 15u;
+                    const uint32_t i0 = tile0 + lw + 4u * (j * 32 + lane);
+                    if (INCR && deltas) {
+                        const uint32_t kb = (d >> (8 * j)) & 15u;
+                        if (__any_sync(0xFFFFFFFFu, rew != 0u || kb != 15u || ((far4 >> j) & 1u))) {
+                            const uint32_t l0 = lw + 4u * (j * 32 + lane);
+                            const bool interior = tile0 + lw + MC_ROWS * 128u + 3u < min(N, limit);
+                            uint32_t s0 = __shfl_up_sync(0xFFFFFFFFu, q[j].w, 1);
+                            uint32_t s5 = __shfl_down_sync(0xFFFFFFFFu, q[j].x, 1);
+                            uint32_t y = 0u, z = 0u;
+                            if (lane == 0) s0 = snapshot(in[(int)l0 - 1]);
+                            if (lane == 31) { s5 = snapshot(in[l0 + 4u]); y = snapshot(in[l0 + 5u]); z = snapshot(in[l0 + 6u]); }
+                            queue_deltas(st, table, dq, s0, q[j], s5, y, z, i0, N, interior, A, B, NW, lane, logC);
+                        }
                     }
-                    rank[j] = run + incl - c;
-                    run += __shfl_sync(0xFFFFFFFFu, incl, 31);
+                    if (rew) {
+                        uint32_t ov[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            if ((rew >> k) & 1u) {
+                                ov[k] = NW | (ov[k] & WORD_START_BIT);
+                                if (LITERAL) src[i0 + k] = ov[k];  // the reference rewrites the source in place
+                            }
+                        }
+                        q[j] = make_uint4(ov[0], ov[1], ov[2], ov[3]);
+                    }
                 }
             }
             if (lane == 0) wsum[sub & 1][warp] = run;
-            __syncthreads();  // warp totals (and, in sub-tile 0, the next ticket) visible; wsum is double-buffered
-            if (sub == 0) next = s_next;
+            __syncthreads();  // every warp has read its part of the sub-tile; warp totals visible (wsum is double-buffered)
             // offset of this warp within the sub-tile, and the sub-tile's kept count
             uint32_t w = lane < MC_WARPS ? wsum[sub & 1][lane] : 0u;
             uint32_t before = lane < warp ? w : 0u;
@@ -708,35 +794,37 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                 w += __shfl_xor_sync(0xFFFFFFFFu, w, o);
             }
             before += acc;
-            // stage the kept symbols at their tile-local rank
-            if (run == MC_ROWS * 128u && (before & 3u) == 0u) {
-                // the whole warp kept everything: ranks are positions, whole 16-byte rows go out
-                uint4* __restrict__ st4 = reinterpret_cast<uint4*>(stage + before);
+            if (untouched) {
+                // (if nothing moved either, the buffer already holds the span where it belongs)
+                if (before != lw) {
+                    if ((before & 3u) == 0u) {
+                        uint4* __restrict__ st4 = reinterpret_cast<uint4*>(in + before);
 #pragma unroll
-                for (int j = 0; j < MC_ROWS; j++) st4[j * 32 + lane] = q[j];
+                        for (int j = 0; j < MC_ROWS; j++) st4[j * 32 + lane] = q[j];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < MC_ROWS; j++) {
+                            uint32_t* o = in + before + 4u * (j * 32 + lane);
+                            o[0] = q[j].x; o[1] = q[j].y; o[2] = q[j].z; o[3] = q[j].w;
+                        }
+                    }
+                }
             } else {
 #pragma unroll
                 for (int j = 0; j < MC_ROWS; j++) {
-                    uint32_t d = before + rank[j];
-                    const uint32_t kb = (keep >> (4 * j)) & 15u;
-                    if (kb & 1u) stage[d++] = q[j].x;
-                    if (kb & 2u) stage[d++] = q[j].y;
-                    if (kb & 4u) stage[d++] = q[j].z;
-                    if (kb & 8u) stage[d++] = q[j].w;
+                    uint32_t o = before + rank[j];
+                    const uint32_t kb = (d >> (8 * j)) & 15u;
+                    if (kb & 1u) in[o++] = q[j].x;
+                    if (kb & 2u) in[o++] = q[j].y;
+                    if (kb & 4u) in[o++] = q[j].z;
+                    if (kb & 8u) in[o++] = q[j].w;
                 }
             }
             acc += w;
-            // the registers are free again: fetch the next sub-tile (of this tile or of the next one)
-            if (sub + 1 < MC_SUBS) load_sub(span_of(tile, sub + 1));
-            else if (next < ntiles) load_sub(span_of(next, 0));
         }
-        const uint32_t agg = acc;
+        PHASE_MARK(3);
         if (warp == 0) {
             uint32_t excl = 0u;
-            if (lane == 0) {
-                const uint32_t flag = tile == 0u ? DESC_PREFIX : DESC_AGG;
-                st_desc(desc + tile, ((unsigned long long)((tag << 2) | flag) << 32) | agg);
-            }
             if (tile != 0u) {
                 bool timed_out = false;
                 excl = lookback(desc, tile, tag, lane, &timed_out);
@@ -757,22 +845,47 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                 }
             }
         }
-        __syncthreads();  // staged run and its base visible
+        __syncthreads();  // compacted run and its base visible
+        PHASE_MARK(4);
         {
+            // Copy-out with 16-byte stores: `head` symbols bring the destination to a 16-byte
+            // boundary, then every store takes its four words from two neighbouring 16-byte rows
+            // of the shared buffer.
             const uint32_t base = s_base;
-            if ((base & 3u) == 0u) {
-                // destination 16-byte aligned: vector stores, then the last few symbols one by one
-                const uint4* __restrict__ st4 = reinterpret_cast<const uint4*>(stage);
-                uint4* __restrict__ d4 = reinterpret_cast<uint4*>(dst + base);
-                for (uint32_t i = threadIdx.x; i < (agg >> 2); i += MC_THREADS) d4[i] = st4[i];
-                for (uint32_t i = (agg & ~3u) + threadIdx.x; i < agg; i += MC_THREADS) dst[base + i] = stage[i];
+            const uint32_t head = min(agg, (4u - (base & 3u)) & 3u);
+            const uint32_t nvec = (agg - head) >> 2;
+            const uint4* __restrict__ in4 = reinterpret_cast<const uint4*>(in);
+            uint4* __restrict__ d4 = reinterpret_cast<uint4*>(dst + base + head);
+            if (threadIdx.x < head) dst[base + threadIdx.x] = in[threadIdx.x];
+            if (head == 0u) {
+                for (uint32_t i = threadIdx.x; i < nvec; i += MC_THREADS) d4[i] = in4[i];
+            } else if (head == 1u) {
+                for (uint32_t i = threadIdx.x; i < nvec; i += MC_THREADS) {
+                    const uint4 lo = in4[i], hi = in4[i + 1];
+                    d4[i] = make_uint4(lo.y, lo.z, lo.w, hi.x);
+                }
+            } else if (head == 2u) {
+                for (uint32_t i = threadIdx.x; i < nvec; i += MC_THREADS) {
+                    const uint4 lo = in4[i], hi = in4[i + 1];
+                    d4[i] = make_uint4(lo.z, lo.w, hi.x, hi.y);
+                }
             } else {
-                for (uint32_t i = threadIdx.x; i < agg; i += MC_THREADS) dst[base + i] = stage[i];
+                for (uint32_t i = threadIdx.x; i < nvec; i += MC_THREADS) {
+                    const uint4 lo = in4[i], hi = in4[i + 1];
+                    d4[i] = make_uint4(lo.w, hi.x, hi.y, hi.z);
+                }
             }
+            for (uint32_t i = head + 4u * nvec + threadIdx.x; i < agg; i += MC_THREADS) dst[base + i] = in[i];
         }
-        __syncthreads();  // the staging area may be reused
+        __syncthreads();  // the buffer may be refilled
+        PHASE_MARK(7);
+#ifdef B200BPE_PHASES
+        ph[6] += 1;
+#endif
         tile = next;
+        if (tile < ntiles) fetch_tile(tile);
     }
+    PHASE_MARK(7);
     if (INCR && deltas) {
         // Fold this CTA's queue segment into the table.  Nobody else reads or writes the segment,
         // the updates commute with those of every other CTA, and doing it here, after the tiles,
@@ -788,6 +901,11 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
         for (uint32_t i = blockIdx.x * MC_THREADS + threadIdx.x; i < C; i += gridDim.x * MC_THREADS)
             t4[i] = make_uint4(0u, 0u, 0u, 0u);
     }
+#ifdef B200BPE_PHASES
+    PHASE_MARK(7);
+    if (threadIdx.x == 0)
+        for (int k = 0; k < 8; k++) atomicAdd(&g_phase_cycles[k], (unsigned long long)ph[k]);
+#endif
 }
 
 // Literal mode with an incrementally maintained table: k_merge_compact accounts for the merge as
