@@ -567,8 +567,8 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
     extern __shared__ __align__(16) uint32_t mc_smem[];  // 4 words (the last: left edge), the tile, 4 words (right edge)
     uint32_t* const in = mc_smem + 4;
     __shared__ __align__(8) unsigned long long bar;
-    __shared__ uint32_t wsum[2][MC_WARPS], wtot[MC_WARPS];
-    __shared__ uint32_t s_tile, s_next, s_base, s_fail;
+    __shared__ uint32_t span_cnt[MC_SUBS * MC_WARPS], lb_sum[MC_WARPS], lb_found[MC_WARPS];
+    __shared__ uint32_t s_tile, s_next, s_fail;
     // `active`, `k3_epoch`, `n[k3_epoch & 1]`, `a`, `b`, `new_id`, `max_count` and `recount` are written
     // by the set-up step only, so every thread of every CTA of this launch reads the same values.
     if (!st->active) return;
@@ -629,256 +629,286 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
         const uint32_t next = s_next;
         const uint32_t tile0 = tile * MC_TILE;  // first symbol of the tile
 
-        // ── pass 1: decide every symbol of the tile (kept? rewritten?) and count ──
-        // Straight-line code over the thread's sixteen rows; per row the decisions fit one byte
-        // (low nibble: own symbol kept, high nibble: own symbol rewritten), so they stay in four
-        // registers for pass 2.  The tile's kept count is published right after this pass, long
-        // before the tile needs its own offset, so the look-back chain runs under pass 2.
-        uint32_t dec[MC_SUBS];   // byte j = decisions of row j of the sub-tile
-        uint32_t far_bits = 0u;  // bit (4 * sub + j), lane 31 only: a pair merges just right of row j's right neighbour
-        uint32_t kept = 0u;
-#pragma unroll
+        // ── pass 1: decide every symbol of the tile (kept? rewritten?) and count; nothing in the
+        // buffer is written, so every neighbour read sees the snapshot.  Straight-line bit logic on
+        // all four rows of a span at once: row j lives in byte j of a word,
+        //   L  bit 8j + k  (k = 0..4): s[k] is `a`             (s[0] = left neighbour, s[1..4] = own)
+        //   R  bit 8j + k  (k = 0..4): s[k + 1] is `b` and does not start a word   (s[5] = right neighbour)
+        //   M = L & R      bit 8j + k: the pair (s[k], s[k + 1]) merges; the symbol at k + 1 is then
+        //                  dropped and the one at k rewritten (train.wgsl:482-497)
+        // so per row the decisions fit one byte (low nibble: own symbol kept, high nibble: own symbol
+        // rewritten) and the four words of a tile stay in registers for pass 2.
+        uint32_t dec0 = 0u, dec1 = 0u, dec2 = 0u, dec3 = 0u;
+#pragma unroll 1
         for (int sub = 0; sub < MC_SUBS; sub++) {
             const uint32_t lw = sub * MC_SUB + warp * (MC_ROWS * 128);  // tile-local first symbol of the warp's span
+            // a warp whose whole span (and the three symbols after it) lies below both N and the
+            // compaction limit needs no bounds tests
             const bool interior = tile0 + lw + MC_ROWS * 128u + 3u < min(N, limit);
-            uint32_t ab[MC_ROWS];  // bits 0..3: own symbol is `a`; bits 4..7: own symbol is `b` and does not start a word
+            uint4 q[MC_ROWS];
+            uint32_t L = 0u, R = 0u;
 #pragma unroll
             for (int j = 0; j < MC_ROWS; j++) {
-                const uint4 q = reinterpret_cast<const uint4*>(in + lw)[j * 32 + lane];
-                ab[j] = ((q.x & TOKEN_MASK) == A ? 1u : 0u) | ((q.y & TOKEN_MASK) == A ? 2u : 0u) |
-                        ((q.z & TOKEN_MASK) == A ? 4u : 0u) | ((q.w & TOKEN_MASK) == A ? 8u : 0u) |
-                        ((q.x & (TOKEN_MASK | WORD_START_BIT)) == B ? 16u : 0u) | ((q.y & (TOKEN_MASK | WORD_START_BIT)) == B ? 32u : 0u) |
-                        ((q.z & (TOKEN_MASK | WORD_START_BIT)) == B ? 64u : 0u) | ((q.w & (TOKEN_MASK | WORD_START_BIT)) == B ? 128u : 0u);
+                q[j] = reinterpret_cast<const uint4*>(in + lw)[j * 32 + lane];
+                L |= ((q[j].x & TOKEN_MASK) == A ? 2u : 0u) << (8 * j);
+                L |= ((q[j].y & TOKEN_MASK) == A ? 4u : 0u) << (8 * j);
+                L |= ((q[j].z & TOKEN_MASK) == A ? 8u : 0u) << (8 * j);
+                L |= ((q[j].w & TOKEN_MASK) == A ? 16u : 0u) << (8 * j);
+                R |= ((q[j].x & (TOKEN_MASK | WORD_START_BIT)) == B ? 1u : 0u) << (8 * j);
+                R |= ((q[j].y & (TOKEN_MASK | WORD_START_BIT)) == B ? 2u : 0u) << (8 * j);
+                R |= ((q[j].z & (TOKEN_MASK | WORD_START_BIT)) == B ? 4u : 0u) << (8 * j);
+                R |= ((q[j].w & (TOKEN_MASK | WORD_START_BIT)) == B ? 8u : 0u) << (8 * j);
             }
-            // the symbol before the span (lane 0) and the three after it (lanes 1..3), as the same kind of bits
+            // the symbol before the span (lane 0) and the three after it (lanes 1..3): bit 0 = is `a`, bit 1 = is a mergeable `b`
             uint32_t edge = 0u;
             if (lane < 4) {
                 const uint32_t v = snapshot(lane == 0 ? in[(int)lw - 1] : in[lw + MC_ROWS * 128u + (lane - 1)]);
-                edge = ((v & TOKEN_MASK) == A ? 1u : 0u) | ((v & (TOKEN_MASK | WORD_START_BIT)) == B ? 16u : 0u);
+                edge = ((v & TOKEN_MASK) == A ? 1u : 0u) | ((v & (TOKEN_MASK | WORD_START_BIT)) == B ? 2u : 0u);
             }
             const uint32_t e_prev = __shfl_sync(0xFFFFFFFFu, edge, 0), e_n0 = __shfl_sync(0xFFFFFFFFu, edge, 1);
             const uint32_t e_n1 = __shfl_sync(0xFFFFFFFFu, edge, 2), e_n2 = __shfl_sync(0xFFFFFFFFu, edge, 3);
-            uint32_t d = 0u;
+            {
+                // left neighbour is `a` → bit 8j; right neighbour is a mergeable `b` → bit 8j + 4
+                const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, L, 1), dn = __shfl_down_sync(0xFFFFFFFFu, R, 1);
+                const uint32_t l31 = __shfl_sync(0xFFFFFFFFu, L, 31), r0 = __shfl_sync(0xFFFFFFFFu, R, 0);
+                uint32_t pa = (up >> 4) & 0x01010101u, nb = (dn << 4) & 0x10101010u;
+                if (lane == 0) pa = ((l31 << 4) & 0x01010100u) | (e_prev & 1u);           // the row before, or the span's left edge
+                if (lane == 31) nb = ((r0 >> 4) & 0x00101010u) | ((e_n0 & 2u) << 27);     // the row after, or the span's right edge
+                L |= pa;
+                R |= nb;
+            }
+            uint32_t M = L & R;
+            uint32_t kb = ~M & 0x0F0F0F0Fu;            // own symbol t (t = 1..4) is dropped iff M[t-1]
+            if (!interior) {
+                // live: bit 8j + k ↔ s[k] exists (k = 0: i0 >= 1; k >= 1: i0 + k - 1 < N); below: own symbol under the compaction limit
+                uint32_t live = 0u, below = 0u;
 #pragma unroll
-            for (int j = 0; j < MC_ROWS; j++) {
-                // left neighbour is `a`?  right neighbour is a mergeable `b`?
-                uint32_t pa = (__shfl_up_sync(0xFFFFFFFFu, ab[j], 1) >> 3) & 1u;
-                uint32_t nb = (__shfl_down_sync(0xFFFFFFFFu, ab[j], 1) >> 4) & 1u;
-                const uint32_t prev_row = j > 0 ? __shfl_sync(0xFFFFFFFFu, ab[j > 0 ? j - 1 : 0], 31) : 0u;
-                const uint32_t next_row = j < MC_ROWS - 1 ? __shfl_sync(0xFFFFFFFFu, ab[j < MC_ROWS - 1 ? j + 1 : j], 0) : 0u;
-                if (lane == 0) pa = j > 0 ? (prev_row >> 3) & 1u : e_prev & 1u;
-                if (lane == 31) nb = j < MC_ROWS - 1 ? (next_row >> 4) & 1u : (e_n0 >> 4) & 1u;
-                const uint32_t left = pa | ((ab[j] & 15u) << 1);          // bit k: s[k] is `a`, k = 0..4
-                const uint32_t right = (ab[j] >> 4) | (nb << 4);           // bit k: s[k + 1] is a mergeable `b`, k = 0..4
-                uint32_t m = left & right;                                 // bit k: pair (s[k], s[k+1]) merges
-                uint32_t kb, rew;
-                if (interior) {
-                    kb = ~m & 15u;             // own symbol t (t = 1..4) is dropped iff m[t-1]
-                    rew = (m >> 1) & 15u;      // and rewritten iff m[t]
-                } else {
+                for (int j = 0; j < MC_ROWS; j++) {
                     const uint32_t i0 = tile0 + lw + 4u * (j * 32 + lane);
-                    uint32_t live = (i0 >= 1u ? 1u : 0u), below = 0u;  // live bit k: s[k] exists (bit 0: i0 >= 1; bit k: i0 + k - 1 < N)
+                    uint32_t lv = (i0 >= 1u ? 1u : 0u), bl = 0u;
 #pragma unroll
-                    for (int k = 1; k < 6; k++) live |= (i0 + k - 1u < N ? 1u : 0u) << k;
+                    for (int k = 1; k < 6; k++) lv |= (i0 + k - 1u < N ? 1u : 0u) << k;
 #pragma unroll
-                    for (int k = 0; k < 4; k++) below |= (i0 + k < limit ? 1u : 0u) << k;
-                    m &= live & (live >> 1);
-                    kb = ~m & 15u & (live >> 1) & below;
-                    rew = (m >> 1) & 15u;
+                    for (int k = 0; k < 4; k++) bl |= (i0 + k < limit ? 1u : 0u) << k;
+                    live |= lv << (8 * j);
+                    below |= bl << (8 * j);
                 }
-                d |= (kb | (rew << 4)) << (8 * j);
-                kept += __popc(kb);
-                if (INCR) {
-                    // lane 31: do the pairs (s[5], y) or (y, z) merge, y and z being the two symbols after s[5]?
-                    // Those are the next row's first three symbols, or the span's right edge.
-                    bool far;
-                    if (j < MC_ROWS - 1) far = ((next_row & 1u) && (next_row & 32u)) || ((next_row & 2u) && (next_row & 64u));
-                    else far = ((e_n0 & 1u) && (e_n1 & 16u)) || ((e_n1 & 1u) && (e_n2 & 16u));
-                    if (!interior) {
-                        const uint32_t i0 = tile0 + lw + 4u * (j * 32 + 31);
-                        if (j < MC_ROWS - 1) far = ((next_row & 1u) && (next_row & 32u) && i0 + 5u < N) || ((next_row & 2u) && (next_row & 64u) && i0 + 6u < N);
-                        else far = ((e_n0 & 1u) && (e_n1 & 16u) && i0 + 5u < N) || ((e_n1 & 1u) && (e_n2 & 16u) && i0 + 6u < N);
+                M &= live & (live >> 1);
+                kb = ~M & 0x0F0F0F0Fu & (live >> 1) & below;
+            }
+            const uint32_t rew = (M >> 1) & 0x0F0F0F0Fu;   // and rewritten iff M[t]
+            const uint32_t d = kb | (rew << 4);
+            if (sub == 0) dec0 = d; else if (sub == 1) dec1 = d; else if (sub == 2) dec2 = d; else dec3 = d;
+            const bool any_m = __any_sync(0xFFFFFFFFu, M != 0u);
+            if (INCR && deltas) {
+                // The pair (t, t+1) changes iff one of the pairs at t-1, t, t+1 merges.  For lanes
+                // 0..30 those are matches some lane of the row sees in its own window; lane 31 also
+                // has to look at the two pairs that begin after its right neighbour: the pairs
+                // (x, y) and (y, z) of the next row's lane 0, or of the symbols after the span.
+                const uint32_t m0 = __shfl_sync(0xFFFFFFFFu, M, 0);
+                uint32_t far = (m0 >> 8) & 0x00060606u;       // rows 0..2: bits 1, 2 of the next row's lane 0
+                {
+                    const uint32_t i5 = tile0 + lw + MC_ROWS * 128u;  // index of the symbol after the span
+                    const bool p1 = (e_n0 & 1u) && (e_n1 & 2u) && (interior || i5 + 1u < N);
+                    const bool p2 = (e_n1 & 1u) && (e_n2 & 2u) && (interior || i5 + 2u < N);
+                    if (p1 || p2) far |= 0x02000000u;
+                }
+                if (lane != 31) far = 0u;
+                if (any_m || __any_sync(0xFFFFFFFFu, far != 0u)) {
+#pragma unroll
+                    for (int j = 0; j < MC_ROWS; j++) {
+                        if (!__any_sync(0xFFFFFFFFu, ((M | far) >> (8 * j)) & 0xFFu)) continue;
+                        const uint32_t l0 = lw + 4u * (j * 32 + lane);
+                        uint32_t s0 = __shfl_up_sync(0xFFFFFFFFu, q[j].w, 1);
+                        uint32_t s5 = __shfl_down_sync(0xFFFFFFFFu, q[j].x, 1);
+                        uint32_t y = 0u, z = 0u;
+                        if (lane == 0) s0 = snapshot(in[(int)l0 - 1]);
+                        if (lane == 31) { s5 = snapshot(in[l0 + 4u]); y = snapshot(in[l0 + 5u]); z = snapshot(in[l0 + 6u]); }
+                        queue_deltas(st, table, dq, s0, q[j], s5, y, z, tile0 + l0, N, interior, A, B, NW, lane, logC);
                     }
-                    if (lane == 31 && far) far_bits |= 1u << (4 * sub + j);
                 }
             }
-            dec[sub] = d;
+            if (LITERAL && any_m) {
+                // the reference rewrites the source in place
+#pragma unroll
+                for (int j = 0; j < MC_ROWS; j++) {
+                    const uint32_t r4 = (rew >> (8 * j)) & 15u;
+                    if (r4) {
+                        uint32_t* o = src + tile0 + lw + 4u * (j * 32 + lane);
+                        if (r4 & 1u) o[0] = NW | (q[j].x & WORD_START_BIT);
+                        if (r4 & 2u) o[1] = NW | (q[j].y & WORD_START_BIT);
+                        if (r4 & 4u) o[2] = NW | (q[j].z & WORD_START_BIT);
+                        if (r4 & 8u) o[3] = NW | (q[j].w & WORD_START_BIT);
+                    }
+                }
+            }
+            // kept symbols of the span
+            uint32_t total = MC_ROWS * 128u;
+            if (__any_sync(0xFFFFFFFFu, kb != 0x0F0F0F0Fu)) {
+                uint32_t c = __popc(kb);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, o);
+                total = c;
+            }
+            if (lane == 0) span_cnt[sub * MC_WARPS + warp] = total;
         }
+        __syncthreads();  // the snapshot has been read by everybody; span counts visible
+        // offsets of the spans within the tile's output, and the tile's kept count
+        uint32_t span_off, span_cnt_reg, agg;
         {
-            // the tile's kept count: warp sums, one barrier, everybody adds the eight sums
-            uint32_t ws = kept;
+            const uint32_t c = span_cnt[lane];   // MC_SUBS * MC_WARPS == 32 spans, in tile order
+            span_cnt_reg = c;
+            uint32_t incl = c;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) ws += __shfl_xor_sync(0xFFFFFFFFu, ws, o);
-            if (lane == 0) wtot[warp] = ws;
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            span_off = incl - c;
+            agg = __shfl_sync(0xFFFFFFFFu, incl, 31);
         }
-        __syncthreads();
-        uint32_t agg = 0u;
-#pragma unroll
-        for (int w = 0; w < MC_WARPS; w++) agg += wtot[w];
         if (threadIdx.x == 0) {
             const uint32_t flag = tile == 0u ? DESC_PREFIX : DESC_AGG;
             st_desc(desc + tile, ((unsigned long long)((tag << 2) | flag) << 32) | agg);
         }
         PHASE_MARK(2);
 
-        // ── pass 2: rank the kept symbols and write them back at their tile-local rank ──
-        uint32_t acc = 0u;  // kept symbols of the sub-tiles done so far (the same in every thread)
+        // ── pass 2: every warp compacts its touched spans in place (a span belongs to one warp) ──
 #pragma unroll 1
         for (int sub = 0; sub < MC_SUBS; sub++) {
+            const uint32_t d = sub == 0 ? dec0 : sub == 1 ? dec1 : sub == 2 ? dec2 : dec3;
+            if (__all_sync(0xFFFFFFFFu, d == 0x0F0F0F0Fu)) continue;
             const uint32_t lw = sub * MC_SUB + warp * (MC_ROWS * 128);
-            const uint32_t d = sub == 0 ? dec[0] : sub == 1 ? dec[1] : sub == 2 ? dec[2] : dec[3];
             uint4 q[MC_ROWS];
 #pragma unroll
             for (int j = 0; j < MC_ROWS; j++) q[j] = reinterpret_cast<const uint4*>(in + lw)[j * 32 + lane];
-            uint32_t rank[MC_ROWS];    // rank of this lane's first kept symbol of row j within the warp's span
-            uint32_t run = MC_ROWS * 128u;
-            const uint32_t far4 = INCR ? (far_bits >> (4 * sub)) & 15u : 0u;
-            // nothing of the warp's span dropped or rewritten (and no delta to queue): ranks are positions
-            const bool untouched = __all_sync(0xFFFFFFFFu, d == 0x0F0F0F0Fu && far4 == 0u);
-            if (!untouched) {
-                // kept counts of the four rows as four byte lanes of one word (a row keeps at most 128, so no lane overflows)
-                uint32_t cnt = 0u;
+            // kept counts of the four rows as four byte lanes of one word (a row keeps at most 128, so no lane overflows)
+            uint32_t cnt = 0u;
 #pragma unroll
-                for (int j = 0; j < MC_ROWS; j++) cnt |= (uint32_t)__popc((d >> (8 * j)) & 15u) << (8 * j);
-                uint32_t incl = cnt;
+            for (int j = 0; j < MC_ROWS; j++) cnt |= (uint32_t)__popc((d >> (8 * j)) & 15u) << (8 * j);
+            uint32_t incl = cnt;
 #pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-                    if (lane >= o) incl += t;
-                }
-                const uint32_t tot = __shfl_sync(0xFFFFFFFFu, incl, 31);
-                run = 0u;
-#pragma unroll
-                for (int j = 0; j < MC_ROWS; j++) {
-                    rank[j] = run + ((incl >> (8 * j)) & 0xFFu) - ((cnt >> (8 * j)) & 0xFFu);
-                    run += (tot >> (8 * j)) & 0xFFu;
-                }
-#pragma unroll
-                for (int j = 0; j < MC_ROWS; j++) {
-                    const uint32_t rew = (d >> (8 * j + 4)) & 15u;
-                    const uint32_t i0 = tile0 + lw + 4u * (j * 32 + lane);
-                    if (INCR && deltas) {
-                        const uint32_t kb = (d >> (8 * j)) & 15u;
-                        if (__any_sync(0xFFFFFFFFu, rew != 0u || kb != 15u || ((far4 >> j) & 1u))) {
-                            const uint32_t l0 = lw + 4u * (j * 32 + lane);
-                            const bool interior = tile0 + lw + MC_ROWS * 128u + 3u < min(N, limit);
-                            uint32_t s0 = __shfl_up_sync(0xFFFFFFFFu, q[j].w, 1);
-                            uint32_t s5 = __shfl_down_sync(0xFFFFFFFFu, q[j].x, 1);
-                            uint32_t y = 0u, z = 0u;
-                            if (lane == 0) s0 = snapshot(in[(int)l0 - 1]);
-                            if (lane == 31) { s5 = snapshot(in[l0 + 4u]); y = snapshot(in[l0 + 5u]); z = snapshot(in[l0 + 6u]); }
-                            queue_deltas(st, table, dq, s0, q[j], s5, y, z, i0, N, interior, A, B, NW, lane, logC);
-                        }
-                    }
-                    if (rew) {
-                        uint32_t ov[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
-#pragma unroll
-                        for (int k = 0; k < 4; k++) {
-                            if ((rew >> k) & 1u) {
-                                ov[k] = NW | (ov[k] & WORD_START_BIT);
-                                if (LITERAL) src[i0 + k] = ov[k];  // the reference rewrites the source in place
-                            }
-                        }
-                        q[j] = make_uint4(ov[0], ov[1], ov[2], ov[3]);
-                    }
-                }
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if (lane >= o) incl += t;
             }
-            if (lane == 0) wsum[sub & 1][warp] = run;
-            __syncthreads();  // every warp has read its part of the sub-tile; warp totals visible (wsum is double-buffered)
-            // offset of this warp within the sub-tile, and the sub-tile's kept count
-            uint32_t w = lane < MC_WARPS ? wsum[sub & 1][lane] : 0u;
-            uint32_t before = lane < warp ? w : 0u;
+            const uint32_t tot = __shfl_sync(0xFFFFFFFFu, incl, 31);
+            __syncwarp();  // all lanes hold their rows: the span may be overwritten
+            uint32_t run = 0u;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                before += __shfl_xor_sync(0xFFFFFFFFu, before, o);
-                w += __shfl_xor_sync(0xFFFFFFFFu, w, o);
+            for (int j = 0; j < MC_ROWS; j++) {
+                const uint32_t kb = (d >> (8 * j)) & 15u, rew = (d >> (8 * j + 4)) & 15u;
+                uint32_t o = lw + run + ((incl >> (8 * j)) & 0xFFu) - ((cnt >> (8 * j)) & 0xFFu);
+                run += (tot >> (8 * j)) & 0xFFu;
+                const uint32_t v0 = (rew & 1u) ? (NW | (q[j].x & WORD_START_BIT)) : q[j].x;
+                const uint32_t v1 = (rew & 2u) ? (NW | (q[j].y & WORD_START_BIT)) : q[j].y;
+                const uint32_t v2 = (rew & 4u) ? (NW | (q[j].z & WORD_START_BIT)) : q[j].z;
+                const uint32_t v3 = (rew & 8u) ? (NW | (q[j].w & WORD_START_BIT)) : q[j].w;
+                if (kb & 1u) in[o++] = v0;
+                if (kb & 2u) in[o++] = v1;
+                if (kb & 4u) in[o++] = v2;
+                if (kb & 8u) in[o++] = v3;
             }
-            before += acc;
-            if (untouched) {
-                // (if nothing moved either, the buffer already holds the span where it belongs)
-                if (before != lw) {
-                    if ((before & 3u) == 0u) {
-                        uint4* __restrict__ st4 = reinterpret_cast<uint4*>(in + before);
-#pragma unroll
-                        for (int j = 0; j < MC_ROWS; j++) st4[j * 32 + lane] = q[j];
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < MC_ROWS; j++) {
-                            uint32_t* o = in + before + 4u * (j * 32 + lane);
-                            o[0] = q[j].x; o[1] = q[j].y; o[2] = q[j].z; o[3] = q[j].w;
-                        }
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < MC_ROWS; j++) {
-                    uint32_t o = before + rank[j];
-                    const uint32_t kb = (d >> (8 * j)) & 15u;
-                    if (kb & 1u) in[o++] = q[j].x;
-                    if (kb & 2u) in[o++] = q[j].y;
-                    if (kb & 4u) in[o++] = q[j].z;
-                    if (kb & 8u) in[o++] = q[j].w;
-                }
-            }
-            acc += w;
         }
         PHASE_MARK(3);
-        if (warp == 0) {
-            uint32_t excl = 0u;
-            if (tile != 0u) {
+
+        // ── the tile's offset: look back over up to 256 predecessors per round, one warp per 32 ──
+        uint32_t excl = 0u;
+        if (tile != 0u) {
+            int pos = (int)tile - 1;
+            for (;;) {
+                const int idx = pos - (warp * 32 + lane);
+                uint32_t hi = (tag << 2) | DESC_PREFIX;  // positions before tile 0 act as a zero prefix
+                uint32_t val = 0u;
                 bool timed_out = false;
-                excl = lookback(desc, tile, tag, lane, &timed_out);
-                if (timed_out && lane == 0) atomicExch(&st->status, (uint32_t)DS_LOOKBACK_TIMEOUT);
-                if (lane == 0) st_desc(desc + tile, ((unsigned long long)((tag << 2) | DESC_PREFIX) << 32) | (excl + agg));
-            }
-            if (lane == 0) {
-                s_base = excl;
-                if (tile == ntiles - 1u) {
-                    // Last tile: publish the new symbol count and advance the epoch.
-                    const uint32_t total = excl + agg;
-                    const uint32_t nnew = N - st->max_count;
-                    if (!LITERAL && total != nnew && st->status == DS_OK && st->world == 1u)
-                        atomicExch(&st->status, (uint32_t)DS_INTERNAL);
-                    st->n[(e + 1u) & 1u] = LITERAL ? nnew : total;
-                    st->v_kept = total;
-                    st->epoch = e + 1u;
+                for (uint32_t spins = 0;; spins++) {
+                    if (idx >= 0) {
+                        const unsigned long long dsc = ld_desc(desc + idx);
+                        hi = (uint32_t)(dsc >> 32);
+                        val = (uint32_t)dsc;
+                    }
+                    const bool ready = ((hi >> 2) == tag) && (hi & 3u) != 0u;
+                    if (__all_sync(0xFFFFFFFFu, ready)) break;
+                    if (spins > LOOKBACK_MAX_SPINS) { timed_out = true; break; }
+                    __nanosleep(20);
                 }
+                const uint32_t pmask = timed_out ? 1u : __ballot_sync(0xFFFFFFFFu, (hi & 3u) == DESC_PREFIX);
+                const int first = pmask ? (__ffs(pmask) - 1) : 32;  // nearest predecessor holding a full prefix
+                uint32_t contrib = (lane <= first && !timed_out) ? val : 0u;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xFFFFFFFFu, contrib, o);
+                if (lane == 0) {
+                    lb_sum[warp] = contrib;
+                    lb_found[warp] = pmask != 0u ? 1u : 0u;
+                    if (timed_out) atomicExch(&st->status, (uint32_t)DS_LOOKBACK_TIMEOUT);
+                }
+                __syncthreads();
+                bool found = false;
+#pragma unroll
+                for (int w = 0; w < MC_WARPS; w++) {
+                    if (!found) {
+                        excl += lb_sum[w];
+                        found = lb_found[w] != 0u;
+                    }
+                }
+                __syncthreads();  // lb_sum / lb_found may be rewritten
+                if (found) break;
+                pos -= MC_THREADS;
             }
         }
-        __syncthreads();  // compacted run and its base visible
+        if (threadIdx.x == 0) {
+            if (tile != 0u) st_desc(desc + tile, ((unsigned long long)((tag << 2) | DESC_PREFIX) << 32) | (excl + agg));
+            if (tile == ntiles - 1u) {
+                // Last tile: publish the new symbol count and advance the epoch.
+                const uint32_t total = excl + agg;
+                const uint32_t nnew = N - st->max_count;
+                if (!LITERAL && total != nnew && st->status == DS_OK && st->world == 1u)
+                    atomicExch(&st->status, (uint32_t)DS_INTERNAL);
+                st->n[(e + 1u) & 1u] = LITERAL ? nnew : total;
+                st->v_kept = total;
+                st->epoch = e + 1u;
+            }
+        }
         PHASE_MARK(4);
-        {
-            // Copy-out with 16-byte stores: `head` symbols bring the destination to a 16-byte
-            // boundary, then every store takes its four words from two neighbouring 16-byte rows
-            // of the shared buffer.
-            const uint32_t base = s_base;
-            const uint32_t head = min(agg, (4u - (base & 3u)) & 3u);
-            const uint32_t nvec = (agg - head) >> 2;
-            const uint4* __restrict__ in4 = reinterpret_cast<const uint4*>(in);
-            uint4* __restrict__ d4 = reinterpret_cast<uint4*>(dst + base + head);
-            if (threadIdx.x < head) dst[base + threadIdx.x] = in[threadIdx.x];
+
+        // ── copy-out: every warp writes its four spans, each a contiguous run, with 16-byte stores:
+        // a few single symbols bring the destination to a 16-byte boundary, then every store takes
+        // its four words from two neighbouring 16-byte rows of the buffer.
+        __syncwarp();  // the warp's own pass-2 writes are visible to all its lanes (tile 0 passes no barrier on the way here)
+#pragma unroll 1
+        for (int sub = 0; sub < MC_SUBS; sub++) {
+            const uint32_t lw = sub * MC_SUB + warp * (MC_ROWS * 128);
+            const uint32_t cnt = __shfl_sync(0xFFFFFFFFu, span_cnt_reg, sub * MC_WARPS + warp);
+            const uint32_t off = excl + __shfl_sync(0xFFFFFFFFu, span_off, sub * MC_WARPS + warp);
+            const uint32_t head = min(cnt, (4u - (off & 3u)) & 3u);
+            const uint32_t nvec = (cnt - head) >> 2;
+            const uint32_t* sp = in + lw;
+            const uint4* sp4 = reinterpret_cast<const uint4*>(sp);
+            uint4* __restrict__ d4 = reinterpret_cast<uint4*>(dst + off + head);
+            if ((uint32_t)lane < head) dst[off + lane] = sp[lane];
             if (head == 0u) {
-                for (uint32_t i = threadIdx.x; i < nvec; i += MC_THREADS) d4[i] = in4[i];
+                for (uint32_t i = lane; i < nvec; i += 32) d4[i] = sp4[i];
             } else if (head == 1u) {
-                for (uint32_t i = threadIdx.x; i < nvec; i += MC_THREADS) {
-                    const uint4 lo = in4[i], hi = in4[i + 1];
+                for (uint32_t i = lane; i < nvec; i += 32) {
+                    const uint4 lo = sp4[i], hi = sp4[i + 1];
                     d4[i] = make_uint4(lo.y, lo.z, lo.w, hi.x);
                 }
             } else if (head == 2u) {
-                for (uint32_t i = threadIdx.x; i < nvec; i += MC_THREADS) {
-                    const uint4 lo = in4[i], hi = in4[i + 1];
+                for (uint32_t i = lane; i < nvec; i += 32) {
+                    const uint4 lo = sp4[i], hi = sp4[i + 1];
                     d4[i] = make_uint4(lo.z, lo.w, hi.x, hi.y);
                 }
             } else {
-                for (uint32_t i = threadIdx.x; i < nvec; i += MC_THREADS) {
-                    const uint4 lo = in4[i], hi = in4[i + 1];
+                for (uint32_t i = lane; i < nvec; i += 32) {
+                    const uint4 lo = sp4[i], hi = sp4[i + 1];
                     d4[i] = make_uint4(lo.w, hi.x, hi.y, hi.z);
                 }
             }
-            for (uint32_t i = head + 4u * nvec + threadIdx.x; i < agg; i += MC_THREADS) dst[base + i] = in[i];
+            const uint32_t done = head + 4u * nvec;
+            if (done + lane < cnt) dst[off + done + lane] = sp[done + lane];
         }
         __syncthreads();  // the buffer may be refilled
-        PHASE_MARK(7);
+        PHASE_MARK(5);
 #ifdef B200BPE_PHASES
         ph[6] += 1;
 #endif
