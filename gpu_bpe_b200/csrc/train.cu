@@ -185,6 +185,7 @@ b200bpe_status Trainer::init_state() {
 }
 
 __global__ void k_begin_batch(DevState* st, uint32_t target) {
+    st->tail_fix = 0u;  // the batch before this one ended with its own k_literal_tail
     st->fill_hwm = 0u;
     st->merges_target = target;
     st->target_hit = (st->merges_done >= target) ? 1u : 0u;
@@ -229,7 +230,6 @@ b200bpe_status Trainer::enqueue_merge(int iter, bool timed) {
         if (literal) k_merge_compact<true, true><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, ktable(), dq);
         else k_merge_compact<false, true><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, ktable(), dq);
         B2_CUDA(ev(5));
-        if (literal) k_literal_tail<<<std::max(1, ctx->sm_count), 256, 0, s>>>(d_state, buf[0], buf[1], ktable());
     } else if (literal) {
         k_merge_compact<true, false><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, ktable(), dq);
     } else {
@@ -305,6 +305,10 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
         } else {
             for (uint32_t i = 0; i < batch; i++) { b200bpe_status r = enqueue_merge((int)i, timed); if (r) return r; }
         }
+        // literal mode, incremental table: inside a batch the next merge's count kernel finishes the
+        // table update of a merge; the batch's last merge gets it here
+        if (incremental && opts.compat_mode == B200BPE_COMPAT_LITERAL)
+            k_literal_tail<<<std::max(1, ctx->sm_count), 256, 0, s>>>(d_state, buf[0], buf[1], ktable());
         // One read-back per batch: the control block and this batch's slice of the merge log
         // (trainer.js:248-267 reads the same two things).
         B2_CUDA(cudaMemcpyAsync(h_state, d_state, sizeof(DevState), cudaMemcpyDeviceToHost, s));

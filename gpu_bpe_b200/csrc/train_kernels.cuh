@@ -66,6 +66,55 @@ __device__ __forceinline__ void table_add(PairSlot* __restrict__ table, uint32_t
     atomicExch(&st->status, (uint32_t)DS_TABLE_FULL);
 }
 
+// Literal mode with an incrementally maintained table: k_merge_compact accounts for the merge as
+// if every kept symbol had been copied; the reference, however, copies only the inputs below
+// limit = N - count and leaves older contents in the rest of the destination (train.wgsl:698,727).
+// This takes out the pairs of the symbols that were not copied and puts in the pairs of what the
+// destination holds instead.  src = the merge's source buffer after its in-place rewrites, dst =
+// its destination; V = symbols copied, N1 = the new symbol count.  Called by every thread of a
+// grid after the merge kernel of that merge and before the next arg-max: by the next merge's
+// count kernel (which has nothing else to do while the table is maintained incrementally), or by
+// k_literal_tail at the end of a batch.  `tail_fix` is rewritten by the next set-up step, after
+// every caller of the grid has read it.
+__device__ __forceinline__ void literal_tail_fix(DevState* __restrict__ st, const uint32_t* buf0, const uint32_t* buf1,
+                                                 PairSlot* table) {
+    if (table == nullptr) table = st->table;
+    const uint32_t e = st->k3_epoch;   // the merge just applied; `epoch` is already one further
+    const uint32_t N = st->n[e & 1], N1 = st->n[(e + 1u) & 1u], V = st->v_kept;
+    const uint32_t* __restrict__ src = (e & 1) ? buf1 : buf0;
+    const uint32_t* __restrict__ dst = (e & 1) ? buf0 : buf1;
+    const uint32_t B = st->b, NW = st->new_id, limit = N - st->max_count;
+    const uint32_t logC = st->table_log2;
+    auto counted = [](uint32_t l, uint32_t r) { return !(r & WORD_START_BIT) && (l & TOKEN_MASK) != 0u && (r & TOKEN_MASK) != 0u; };
+    auto emit = [&](uint32_t l, uint32_t r, uint32_t delta) {
+        const unsigned long long key = ((unsigned long long)(l & TOKEN_MASK) << 32) | (r & TOKEN_MASK);
+        table_add(table, logC, key, hash_pair(key), delta, st);
+    };
+    // a position of the source is dropped iff its left neighbour was rewritten to the new symbol
+    auto dropped = [&](uint32_t i) { return i > 0u && i < N && (src[i - 1u] & TOKEN_MASK) == NW && !(src[i] & WORD_START_BIT) &&
+                                            (src[i] & TOKEN_MASK) == B; };
+    const uint32_t gtid = blockIdx.x * blockDim.x + threadIdx.x, gstride = gridDim.x * blockDim.x;
+    // (1) pairs whose left symbol is a kept source position >= limit: they were counted, but never copied
+    for (uint32_t i = limit + gtid; i < N; i += gstride) {
+        if (dropped(i)) continue;
+        const uint32_t r = (i + 1u < N && dropped(i + 1u)) ? i + 2u : i + 1u;
+        if (r < N && counted(src[i], src[r])) emit(src[i], src[r], 0xFFFFFFFFu);
+    }
+    // (2) the pair that joined the last copied symbol to the first kept source position >= limit
+    if (gtid == 0 && V > 0u) {
+        const uint32_t z0 = dropped(limit) ? limit + 1u : limit;
+        if (z0 < N && counted(dst[V - 1u], src[z0])) emit(dst[V - 1u], src[z0], 0xFFFFFFFFu);
+    }
+    // (3) the pairs of what the destination really holds from the last copied symbol on
+    for (uint32_t u = (V > 0u ? V - 1u : 0u) + gtid; u + 1u < N1; u += gstride)
+        if (counted(dst[u], dst[u + 1u])) emit(dst[u], dst[u + 1u], 1u);
+}
+
+__global__ void __launch_bounds__(256)
+k_literal_tail(DevState* __restrict__ st, const uint32_t* buf0, const uint32_t* buf1, PairSlot* table) {
+    if (st->tail_fix) literal_tail_fix(st, buf0, buf1, table);
+}
+
 // ─────────────────────────────── pair count ───────────────────────────────
 // Each CTA owns one contiguous span of the symbol array and reads it with 16-byte loads.
 // Pairs are first aggregated in a shared-memory table: 32-bit keys (left << 16 | right) and
@@ -106,9 +155,14 @@ k_pair_count(DevState* __restrict__ st, const uint32_t* __restrict__ buf0, const
 
     // One thread reads the stop flags for the whole CTA: `status` can change while this kernel
     // runs (another CTA may find the table full), and a CTA must not split at a barrier.
-    __shared__ uint32_t s_idle;
-    if (threadIdx.x == 0) s_idle = st->early_stop | st->target_hit | st->status | (st->incremental & (st->recount ^ 1u));
+    __shared__ uint32_t s_idle, s_tail;
+    if (threadIdx.x == 0) {
+        s_idle = st->early_stop | st->target_hit | st->status | (st->incremental & (st->recount ^ 1u));
+        s_tail = st->tail_fix;
+    }
     __syncthreads();
+    // literal mode, incremental table: finish the table update of the merge before this one
+    if (s_tail) literal_tail_fix(st, buf0, buf1, table);
     if (s_idle) return;
     for (int i = threadIdx.x; i < 2 * S; i += THREADS) skey[i] = 0u;
     __syncthreads();
@@ -382,7 +436,7 @@ struct DeltaQueues {
     uint32_t segments;  // number of segments = CTAs of the merge kernel
 };
 
-__device__ __noinline__ void queue_deltas(DevState* st, PairSlot* __restrict__ table, DeltaQueues dq, uint32_t s0, uint4 own,
+__device__ __noinline__ void queue_deltas(DevState* st, PairSlot* __restrict__ table, DeltaQueues dq, uint32_t* qcnt, uint32_t s0, uint4 own,
                                           uint32_t s5, uint32_t y31, uint32_t z31, uint32_t i0, uint32_t N, bool interior,
                                           uint32_t A, uint32_t B, uint32_t NW, int lane, uint32_t logC) {
     uint32_t s[8] = {s0, own.x, own.y, own.z, own.w, s5, 0u, 0u};
@@ -439,8 +493,8 @@ __device__ __noinline__ void queue_deltas(DevState* st, PairSlot* __restrict__ t
     }
     uint32_t base_m = 0u, base_p = 0u;
     if (lane == 31) {
-        if (im) base_m = atomicAdd(&dq.counts[2u * blockIdx.x], im);
-        if (ip) base_p = atomicAdd(&dq.counts[2u * blockIdx.x + 1u], ip);
+        if (im) base_m = atomicAdd(&qcnt[0], im);
+        if (ip) base_p = atomicAdd(&qcnt[1], ip);
     }
     base_m = __shfl_sync(0xFFFFFFFFu, base_m, 31) + im - cm;
     base_p = __shfl_sync(0xFFFFFFFFu, base_p, 31) + ip - cp;
@@ -470,10 +524,10 @@ __device__ __noinline__ void queue_deltas(DevState* st, PairSlot* __restrict__ t
 // Fold one queue segment into the table (the whole CTA takes part).  Equal keys held by the lanes
 // of a warp are combined first (match-any), so a popular neighbour pair costs one atomic per warp.
 // The segment's counters are cleared at the end.
-__device__ __forceinline__ void apply_segment(DevState* st, DeltaQueues dq, uint32_t g, PairSlot* __restrict__ table,
+__device__ __forceinline__ void apply_segment(DevState* st, DeltaQueues dq, const uint32_t* qcnt, uint32_t g, PairSlot* __restrict__ table,
                                               uint32_t logC) {
     const int lane = threadIdx.x & 31;
-    const uint32_t nm = min(dq.counts[2u * g], dq.seg_cap), np = min(dq.counts[2u * g + 1u], dq.seg_cap);
+    const uint32_t nm = min(qcnt[0], dq.seg_cap), np = min(qcnt[1], dq.seg_cap);
     const uint32_t total = nm + np;
     if (total == 0u) return;
     const uint32_t* __restrict__ seg_m = dq.minus + (size_t)g * dq.seg_cap;
@@ -495,8 +549,6 @@ __device__ __forceinline__ void apply_segment(DevState* st, DeltaQueues dq, uint
             }
         }
     }
-    __syncthreads();
-    if (threadIdx.x == 0) { dq.counts[2u * g] = 0u; dq.counts[2u * g + 1u] = 0u; }
 }
 
 // ── asynchronous bulk copy global → shared memory (one per tile), completion on an mbarrier ──
@@ -569,6 +621,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
     __shared__ __align__(8) unsigned long long bar;
     __shared__ uint32_t span_cnt[MC_SUBS * MC_WARPS], lb_sum[MC_WARPS], lb_found[MC_WARPS];
     __shared__ uint32_t s_tile, s_next, s_fail;
+    __shared__ uint32_t s_qcnt[2];  // entries reserved in this CTA's segments of the minus and plus queues
     // `active`, `k3_epoch`, `n[k3_epoch & 1]`, `a`, `b`, `new_id`, `max_count` and `recount` are written
     // by the set-up step only, so every thread of every CTA of this launch reads the same values.
     if (!st->active) return;
@@ -585,6 +638,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
     const uint32_t logC = st->table_log2;
     if (table == nullptr) table = st->table;
     auto snapshot = [&](uint32_t v) { return (v & TOKEN_MASK) == NW ? ((v & WORD_START_BIT) | A) : v; };
+    const uint32_t AB = A | (B << 16);  // the low halves of a pair that may merge
 
     // Start the copy of a tile: thread 0 issues the bulk copy, threads 32..35 fetch the edges.
     // Callers make sure (barrier) that nobody still reads the buffer.
@@ -606,6 +660,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
         mbar_init(&bar, 1u);
         fence_proxy_async_smem();
         s_fail = 0u;
+        s_qcnt[0] = s_qcnt[1] = 0u;
         s_tile = atomicAdd(&st->ticket, 1u);
     }
     __syncthreads();
@@ -646,10 +701,33 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
             // compaction limit needs no bounds tests
             const bool interior = tile0 + lw + MC_ROWS * 128u + 3u < min(N, limit);
             uint4 q[MC_ROWS];
+#pragma unroll
+            for (int j = 0; j < MC_ROWS; j++) q[j] = reinterpret_cast<const uint4*>(in + lw)[j * 32 + lane];
+            // Candidate test first: two neighbouring symbols can only merge if their low halves are
+            // (a, b), one byte permute and one compare per pair.  Every lane tests the four pairs that
+            // begin at its own symbols; lane 0 adds the pair that begins at the symbol before the span,
+            // lane 31 (when deltas are queued) the two pairs that begin right after it.  A span
+            // without a candidate, which is most of them, keeps everything and skips the bit logic.
+            bool cand = false;
+#pragma unroll
+            for (int j = 0; j < MC_ROWS; j++) {
+                uint32_t nx = __shfl_down_sync(0xFFFFFFFFu, q[j].x, 1);
+                const uint32_t rx = __shfl_sync(0xFFFFFFFFu, q[j < MC_ROWS - 1 ? j + 1 : j].x, 0);
+                if (lane == 31) nx = j < MC_ROWS - 1 ? rx : snapshot(in[lw + MC_ROWS * 128u]);
+                cand |= __byte_perm(q[j].x, q[j].y, 0x5410) == AB || __byte_perm(q[j].y, q[j].z, 0x5410) == AB ||
+                        __byte_perm(q[j].z, q[j].w, 0x5410) == AB || __byte_perm(q[j].w, nx, 0x5410) == AB;
+            }
+            if (lane == 0) cand |= __byte_perm(snapshot(in[(int)lw - 1]), q[0].x, 0x5410) == AB;
+            if (INCR && lane == 31) {
+                const uint32_t n0 = snapshot(in[lw + MC_ROWS * 128u]), n1 = snapshot(in[lw + MC_ROWS * 128u + 1u]);
+                const uint32_t n2 = snapshot(in[lw + MC_ROWS * 128u + 2u]);
+                cand |= __byte_perm(n0, n1, 0x5410) == AB || __byte_perm(n1, n2, 0x5410) == AB;
+            }
+            uint32_t kb = 0x0F0F0F0Fu, rew = 0u;   // per row one byte: own symbol kept (low nibble), rewritten (high nibble)
+            if (!interior || __any_sync(0xFFFFFFFFu, cand)) {
             uint32_t L = 0u, R = 0u;
 #pragma unroll
             for (int j = 0; j < MC_ROWS; j++) {
-                q[j] = reinterpret_cast<const uint4*>(in + lw)[j * 32 + lane];
                 L |= ((q[j].x & TOKEN_MASK) == A ? 2u : 0u) << (8 * j);
                 L |= ((q[j].y & TOKEN_MASK) == A ? 4u : 0u) << (8 * j);
                 L |= ((q[j].z & TOKEN_MASK) == A ? 8u : 0u) << (8 * j);
@@ -678,7 +756,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                 R |= nb;
             }
             uint32_t M = L & R;
-            uint32_t kb = ~M & 0x0F0F0F0Fu;            // own symbol t (t = 1..4) is dropped iff M[t-1]
+            kb = ~M & 0x0F0F0F0Fu;                     // own symbol t (t = 1..4) is dropped iff M[t-1]
             if (!interior) {
                 // live: bit 8j + k ↔ s[k] exists (k = 0: i0 >= 1; k >= 1: i0 + k - 1 < N); below: own symbol under the compaction limit
                 uint32_t live = 0u, below = 0u;
@@ -696,9 +774,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                 M &= live & (live >> 1);
                 kb = ~M & 0x0F0F0F0Fu & (live >> 1) & below;
             }
-            const uint32_t rew = (M >> 1) & 0x0F0F0F0Fu;   // and rewritten iff M[t]
-            const uint32_t d = kb | (rew << 4);
-            if (sub == 0) dec0 = d; else if (sub == 1) dec1 = d; else if (sub == 2) dec2 = d; else dec3 = d;
+            rew = (M >> 1) & 0x0F0F0F0Fu;              // and rewritten iff M[t]
             const bool any_m = __any_sync(0xFFFFFFFFu, M != 0u);
             if (INCR && deltas) {
                 // The pair (t, t+1) changes iff one of the pairs at t-1, t, t+1 merges.  For lanes
@@ -724,7 +800,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                         uint32_t y = 0u, z = 0u;
                         if (lane == 0) s0 = snapshot(in[(int)l0 - 1]);
                         if (lane == 31) { s5 = snapshot(in[l0 + 4u]); y = snapshot(in[l0 + 5u]); z = snapshot(in[l0 + 6u]); }
-                        queue_deltas(st, table, dq, s0, q[j], s5, y, z, tile0 + l0, N, interior, A, B, NW, lane, logC);
+                        queue_deltas(st, table, dq, s_qcnt, s0, q[j], s5, y, z, tile0 + l0, N, interior, A, B, NW, lane, logC);
                     }
                 }
             }
@@ -741,6 +817,11 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                         if (r4 & 8u) o[3] = NW | (q[j].w & WORD_START_BIT);
                     }
                 }
+            }
+            }
+            {
+                const uint32_t d = kb | (rew << 4);
+                if (sub == 0) dec0 = d; else if (sub == 1) dec1 = d; else if (sub == 2) dec2 = d; else dec3 = d;
             }
             // kept symbols of the span
             uint32_t total = MC_ROWS * 128u;
@@ -921,7 +1002,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
         // the updates commute with those of every other CTA, and doing it here, after the tiles,
         // keeps the scattered table traffic out of the streaming loop without another launch.
         __syncthreads();
-        apply_segment(st, dq, blockIdx.x, table, logC);
+        apply_segment(st, dq, s_qcnt, blockIdx.x, table, logC);
     }
     if (INCR && !deltas) {
         // a == b (or a rebuild is already due): no deltas were written, so nobody else touches the
@@ -936,48 +1017,6 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
     if (threadIdx.x == 0)
         for (int k = 0; k < 8; k++) atomicAdd(&g_phase_cycles[k], (unsigned long long)ph[k]);
 #endif
-}
-
-// Literal mode with an incrementally maintained table: k_merge_compact accounts for the merge as
-// if every kept symbol had been copied; the reference, however, copies only the inputs below
-// limit = N - count and leaves older contents in the rest of the destination (train.wgsl:698,727).
-// This kernel takes out the pairs of the symbols that were not copied and puts in the pairs of
-// what the destination holds instead.  src = the merge's source buffer after its in-place
-// rewrites, dst = its destination; V = symbols copied, N1 = the new symbol count.
-__global__ void __launch_bounds__(256)
-k_literal_tail(DevState* __restrict__ st, const uint32_t* buf0, const uint32_t* buf1, PairSlot* table) {
-    // runs right after k_merge_compact of the same merge: k3_epoch is that merge, epoch already advanced
-    if (!st->tail_fix) return;
-    if (table == nullptr) table = st->table;
-    const uint32_t e = st->k3_epoch;
-    const uint32_t N = st->n[e & 1], N1 = st->n[(e + 1u) & 1u], V = st->v_kept;
-    const uint32_t* __restrict__ src = (e & 1) ? buf1 : buf0;
-    const uint32_t* __restrict__ dst = (e & 1) ? buf0 : buf1;
-    const uint32_t B = st->b, NW = st->new_id, limit = N - st->max_count;
-    const uint32_t logC = st->table_log2;
-    auto counted = [](uint32_t l, uint32_t r) { return !(r & WORD_START_BIT) && (l & TOKEN_MASK) != 0u && (r & TOKEN_MASK) != 0u; };
-    auto emit = [&](uint32_t l, uint32_t r, uint32_t delta) {
-        const unsigned long long key = ((unsigned long long)(l & TOKEN_MASK) << 32) | (r & TOKEN_MASK);
-        table_add(table, logC, key, hash_pair(key), delta, st);
-    };
-    // a position of the source is dropped iff its left neighbour was rewritten to the new symbol
-    auto dropped = [&](uint32_t i) { return i > 0u && i < N && (src[i - 1u] & TOKEN_MASK) == NW && !(src[i] & WORD_START_BIT) &&
-                                            (src[i] & TOKEN_MASK) == B; };
-    const uint32_t gtid = blockIdx.x * blockDim.x + threadIdx.x, gstride = gridDim.x * blockDim.x;
-    // (1) pairs whose left symbol is a kept source position >= limit: they were counted, but never copied
-    for (uint32_t i = limit + gtid; i < N; i += gstride) {
-        if (dropped(i)) continue;
-        const uint32_t r = (i + 1u < N && dropped(i + 1u)) ? i + 2u : i + 1u;
-        if (r < N && counted(src[i], src[r])) emit(src[i], src[r], 0xFFFFFFFFu);
-    }
-    // (2) the pair that joined the last copied symbol to the first kept source position >= limit
-    if (gtid == 0 && V > 0u) {
-        const uint32_t z0 = dropped(limit) ? limit + 1u : limit;
-        if (z0 < N && counted(dst[V - 1u], src[z0])) emit(dst[V - 1u], src[z0], 0xFFFFFFFFu);
-    }
-    // (3) the pairs of what the destination really holds from the last copied symbol on
-    for (uint32_t u = (V > 0u ? V - 1u : 0u) + gtid; u + 1u < N1; u += gstride)
-        if (counted(dst[u], dst[u + 1u])) emit(dst[u], dst[u + 1u], 1u);
 }
 
 // ─────────────────────────────── symbol buffer set-up ───────────────────────────────
