@@ -5,7 +5,7 @@
 N = 1 workload: train 8,000 merges on 64 MiB of seeded synthetic UTF-8 text (the second benchmark
 configuration); one step = one complete training run (re-tag the resident corpus, run the merge
 loop).  N > 1 (under torchrun): the same corpus cut at word starts across the ranks, "fixed"
-compaction mode, one NCCL count exchange + one 24-byte all-reduce per merge (strong scaling).
+compaction mode, one NCCL count exchange + one 32-byte all-reduce per merge (strong scaling).
 
 One JSON line on stdout:
   value        merges/s with the corpus resident in HBM (CUDA events on the library's stream)
@@ -41,6 +41,11 @@ ENCODE_BYTES = 256 * MIB
 ENCODE_DOCS = 65536
 METRIC = "train_merges_per_s"
 WORKLOAD = "config2: 8,000 merges on 64 MiB synthetic UTF-8 (seed 2, 50k-word per-script Zipf 1.1 lexicons)"
+# DRAM bytes (read + write) per algorithmic byte, from one ncu capture of each kernel (the
+# summaries under profiles/ give the commands): the roofline "traffic" is this ratio times the
+# algorithmic bytes of an average launch of the run.  Below 1 where the 126 MB L2 keeps part of the
+# symbol array from one merge to the next.
+NCU_DRAM_PER_ALGORITHMIC_BYTE = {"pair_count": 1.02, "argmax": 1.00, "merge_compact": 0.64, "trie_walk": 1.05}
 
 
 def measured_hbm_peak():
@@ -245,7 +250,10 @@ def main():
                             "avg_us": 1e3 * ks["exchange_ms"] / max(1, ks["exchange_launches"])}
     dom = max(("pair_count", "argmax", "merge_compact"), key=lambda k: kern[k]["ms_total"])
     roofline = {"bound": "hbm", "kernel": "k_" + dom, "achieved": kern[dom]["achieved_GBps"], "peak": peak, "unit": "GB/s",
-                "frac": kern[dom]["frac_of_peak"], "traffic": None, "peak_source": peak_src,
+                "frac": kern[dom]["frac_of_peak"], "peak_source": peak_src,
+                "traffic": NCU_DRAM_PER_ALGORITHMIC_BYTE[dom] * kern[dom]["algorithmic_GB"] * 1e9 / max(1, kern[dom]["launches"]),
+                "traffic_how": "DRAM read + write bytes per launch: the ncu ratio of DRAM to algorithmic bytes for this kernel "
+                               "(merge 3,000 of this workload for k_merge_compact) x the algorithmic bytes of an average launch",
                 "per_launch_algorithmic_bytes": kern[dom]["algorithmic_GB"] * 1e9 / max(1, kern[dom]["launches"]),
                 "avg_launch_us": kern[dom]["avg_us"], "kernels": kern,
                 "how": "one extra run with CUDA events around every kernel on the library's stream (no graph)"}
@@ -337,7 +345,8 @@ def main():
                   "e2e_h2d_bytes": int(b1 - b0 + 8 * (d1 - d0 + 1)), "e2e_d2h_bytes": int(4 * ntok + 8 * (d1 - d0 + 1)),
                   "roofline": {"bound": "hbm", "kernel": "k_trie_walk", "achieved": alg_bytes / 1e9 / (w_ms / 1e3),
                                "peak": peak, "unit": "GB/s", "frac": alg_bytes / 1e9 / (w_ms / 1e3) / peak,
-                               "traffic": None, "algorithmic_bytes": "L input bytes + 4 T token bytes (this rank)"}}
+                               "traffic": NCU_DRAM_PER_ALGORITHMIC_BYTE["trie_walk"] * alg_bytes,
+                               "algorithmic_bytes": "L input bytes + 4 T token bytes (this rank)"}}
         tok.destroy()
 
     cpu = None
