@@ -138,7 +138,7 @@ def run_reference(args):
 
 
 def main():
-    global MERGES, CORPUS_BYTES
+    global MERGES, CORPUS_BYTES, ENCODE_BYTES, ENCODE_DOCS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2)
@@ -150,9 +150,12 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--merges", type=int, default=MERGES, help="for experiments only; the benchmark is 8,000")
     ap.add_argument("--corpus-mib", type=int, default=CORPUS_BYTES // MIB, help="for experiments only; the benchmark is 64")
+    ap.add_argument("--encode-mib", type=int, default=ENCODE_BYTES // MIB, help="for experiments only; the benchmark is 256")
+    ap.add_argument("--encode-docs", type=int, default=ENCODE_DOCS, help="for experiments only; the benchmark is 65,536")
     ap.add_argument("--mode", default=None, help="literal | fixed (default: literal on 1 GPU, fixed when sharded)")
     args = ap.parse_args()
     MERGES, CORPUS_BYTES = args.merges, args.corpus_mib * MIB
+    ENCODE_BYTES, ENCODE_DOCS = args.encode_mib * MIB, args.encode_docs
     if args.impl == "reference":
         return run_reference(args)
 
