@@ -55,9 +55,23 @@ struct DevState {
     uint32_t v_kept;        // symbols the last merge copied to the destination buffer
     uint32_t tail_fix;      // literal + incremental: the tail fix-up kernel has work for the merge just applied
     uint32_t fill_hwm;      // sharded runs: largest exchange-bucket fill seen on any rank since the batch began
-    uint32_t pad[3];
+    // Candidate list of the arg-max (incremental table only): the slots whose count was at least
+    // cand_tau at the last full scan of the table, plus every slot whose count has crossed cand_tau
+    // upwards since.  While the best listed count is >= cand_tau the list holds the global best.
+    uint32_t need_scan;     // the next arg-max must scan the whole table (and rebuild the list)
+    uint32_t cand_n;        // entries appended to the list (may exceed its capacity: then it is void)
+    uint32_t cand_tau;      // threshold of the list; 0xFFFFFFFF = no list, nothing is appended
+    uint32_t cand_tau_next; // threshold the next full scan will use
+    uint32_t since_scan;    // merges since the last full scan
+    uint32_t full_scans;    // full scans since creation/reset (statistics)
+    uint32_t k1_done;       // CTAs of the count kernel that have finished (when its last CTA picks the next merge)
     PairSlot* table;        // the pair table (kept here so that replacing it does not invalidate a captured graph)
+    uint32_t* cand;         // the candidate list: slot indices
+    uint32_t presetup;      // the count kernel has already chosen and set up this iteration's merge: the arg-max kernel skips
+    uint32_t pad[3];
 };
+constexpr uint32_t CAND_CAP = 1u << 13;      // entries of the candidate list (one CTA scans it)
+constexpr uint32_t CAND_MAX_AGE = 512;       // merges after which a full scan is due anyway (refreshes the table's fill)
 
 struct CtaBest {
     unsigned long long key;

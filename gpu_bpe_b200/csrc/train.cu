@@ -48,6 +48,7 @@ struct Trainer {
     uint32_t* d_log = nullptr;
     uint32_t* h_log = nullptr;    // pinned
     CtaBest* d_cta_best = nullptr;
+    uint32_t* d_cand = nullptr;   // candidate list of the arg-max (slot indices)
     unsigned long long* d_desc = nullptr;
     DeltaQueues dq{nullptr, nullptr, nullptr, 0, 0};  // incremental mode only
     Exchange xch;                 // sharded runs only
@@ -83,7 +84,7 @@ Trainer::~Trainer() {
     if (own_inputs) { cudaFree(d_bytes); cudaFree(d_mask); }
     cudaFree(d_sym_init);
     cudaFree(buf[0]); cudaFree(buf[1]); cudaFree(table); cudaFree(d_state); cudaFree(d_log);
-    cudaFree(d_cta_best); cudaFree(d_desc); cudaFree(dq.minus); cudaFree(dq.plus); cudaFree(dq.counts);
+    cudaFree(d_cta_best); cudaFree(d_desc); cudaFree(d_cand); cudaFree(dq.minus); cudaFree(dq.plus); cudaFree(dq.counts);
     xch.release();
     if (h_state) cudaFreeHost(h_state);
     if (h_log) cudaFreeHost(h_log);
@@ -113,6 +114,7 @@ b200bpe_status Trainer::alloc_common() {
     const uint64_t ntiles = (n0 + MC_TILE - 1) / MC_TILE;
     grid_mc = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)sms * 3, ntiles));
     B2_CUDA(cudaMalloc(&d_cta_best, sizeof(CtaBest) * (size_t)(sms * 4 + 1)));
+    B2_CUDA(cudaMalloc(&d_cand, sizeof(uint32_t) * CAND_CAP));
     B2_CUDA(cudaMalloc(&d_desc, sizeof(unsigned long long) * (ntiles + 1)));
     B2_CUDA(cudaMemsetAsync(d_desc, 0, sizeof(unsigned long long) * (ntiles + 1), ctx->stream));
     if (incremental) {
@@ -169,6 +171,10 @@ b200bpe_status Trainer::init_state() {
     h_state->incremental = incremental ? 1u : 0u;
     h_state->recount = 1u;
     h_state->table = table;
+    h_state->need_scan = 1u;
+    h_state->cand_tau = 0xFFFFFFFFu;
+    h_state->cand_tau_next = 0xFFFFFFFFu;
+    h_state->cand = d_cand;
     B2_CUDA(cudaMemcpyAsync(d_state, h_state, sizeof(DevState), cudaMemcpyHostToDevice, s));
     B2_CUDA(cudaEventRecord(ev_run1, s));
     B2_CUDA(cudaStreamSynchronize(s));
@@ -196,6 +202,9 @@ __global__ void k_clear_status(DevState* st, uint32_t table_log2, PairSlot* tabl
     st->table_log2 = table_log2;
     st->table = table;
     st->recount = 1u;  // the table is new and empty
+    st->need_scan = 1u;
+    st->cand_tau = 0xFFFFFFFFu;
+    st->cand_n = 0u;
 }
 
 // One merge iteration on the stream.  `timed` brackets each kernel with events.
@@ -213,7 +222,7 @@ b200bpe_status Trainer::enqueue_merge(int iter, bool timed) {
         fflush(stderr);
     };
     B2_CUDA(ev(0));
-    k_pair_count<PC_SLOTS, PC_THREADS><<<grid_pc, PC_THREADS, PC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], ktable());
+    k_pair_count<PC_SLOTS, PC_THREADS><<<grid_pc, PC_THREADS, PC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], ktable(), d_log);
     B2_CUDA(ev(1));
     dsync("pair_count");
     if (ctx->world > 1) {
@@ -242,13 +251,15 @@ b200bpe_status Trainer::enqueue_merge(int iter, bool timed) {
     return B200BPE_OK;
 }
 
+constexpr uint32_t SPARE_ITERS = 4;   // iterations beyond the batch size, for arg-max passes that only void their candidate list
+
 b200bpe_status Trainer::build_graph() {
     if (graph) { cudaGraphExecDestroy(graph); graph = nullptr; }
     cudaStream_t s = ctx->stream;
     cudaGraph_t g = nullptr;
     B2_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
     b200bpe_status r = B200BPE_OK;
-    for (uint32_t i = 0; i < opts.batch_merges && r == B200BPE_OK; i++) r = enqueue_merge((int)i, false);
+    for (uint32_t i = 0; i < opts.batch_merges + SPARE_ITERS && r == B200BPE_OK; i++) r = enqueue_merge((int)i, false);
     cudaError_t e = cudaStreamEndCapture(s, &g);
     if (r != B200BPE_OK) { if (g) cudaGraphDestroy(g); return r; }
     B2_CUDA(e);
@@ -288,22 +299,33 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
     if (max_merges && max_merges < remaining) remaining = max_merges;
     const uint32_t start_done = merges_done;
     if (timed && kev.empty()) {
-        kev.resize((size_t)opts.batch_merges * 8);
+        kev.resize((size_t)(opts.batch_merges + SPARE_ITERS) * 8);
         for (auto& e : kev) B2_CUDA(cudaEventCreate(&e));
     }
     auto t0 = std::chrono::steady_clock::now();
     B2_CUDA(cudaEventRecord(ev_run0, s));
-    int grow_retries = 0;
+    int grow_retries = 0, idle_batches = 0;
+    uint32_t full_scans_seen = 0;
+    {
+        B2_CUDA(cudaMemcpyAsync(h_state, d_state, sizeof(DevState), cudaMemcpyDeviceToHost, s));
+        B2_CUDA(cudaStreamSynchronize(s));
+        full_scans_seen = h_state->full_scans;
+    }
     bool table_replaced = false;
+    // A batch ends at an absolute merge index (progress is reported there, as the reference does
+    // every 128 merges); an arg-max that finds its candidate list stale uses up an iteration without
+    // a merge, so the graph holds a few spare iterations and a batch that still falls short is continued.
+    uint32_t batch_target = merges_done;
     while (remaining > 0 && !early_stop) {
-        const uint32_t batch = std::min(opts.batch_merges, remaining);
+        if (merges_done >= batch_target) batch_target = merges_done + std::min(opts.batch_merges, remaining);
         const uint32_t before = merges_done;
-        k_begin_batch<<<1, 1, 0, s>>>(d_state, before + batch);
+        const uint32_t batch = batch_target - before;
+        k_begin_batch<<<1, 1, 0, s>>>(d_state, batch_target);
         if (use_graph) {
             if (!graph) { b200bpe_status r = build_graph(); if (r) return r; }
             B2_CUDA(cudaGraphLaunch(graph, s));
         } else {
-            for (uint32_t i = 0; i < batch; i++) { b200bpe_status r = enqueue_merge((int)i, timed); if (r) return r; }
+            for (uint32_t i = 0; i < batch + SPARE_ITERS; i++) { b200bpe_status r = enqueue_merge((int)i, timed); if (r) return r; }
         }
         // literal mode, incremental table: inside a batch the next merge's count kernel finishes the
         // table update of a merge; the batch's last merge gets it here
@@ -319,7 +341,7 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
         const uint32_t got = done_now - before;
         if (timed) {
             uint64_t nk = cur_n;
-            for (uint32_t i = 0; i < batch; i++) {
+            for (uint32_t i = 0; i < batch + SPARE_ITERS; i++) {   // (an iteration without a merge shifts the attribution of the ones after it: statistics only)
                 float ms = 0;
                 const size_t b = (size_t)i * 8;
                 const bool merged = i < got;
@@ -340,7 +362,7 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
                 cudaEventElapsedTime(&ms, kev[b + 5], kev[b + 4]); stats.table_update_ms += ms;
                 stats.argmax_launches++; stats.merge_compact_launches++;
                 if (ctx->world > 1) stats.exchange_launches++;
-                stats.argmax_bytes += 24ull << table_log2;
+                if (!incremental) stats.argmax_bytes += 24ull << table_log2;  // read 16 B per slot, clear the 8 B key
                 if (merged) {
                     const uint64_t nn = (ctx->world > 1) ? nk : nk - h_log[(size_t)(before + i) * 4 + 3];
                     stats.merge_compact_bytes += 4ull * nk + 4ull * nn;
@@ -355,9 +377,20 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
             if (counts_out) counts_out[o] = l[3];
         }
         if (got == 0 && !h_state->early_stop && h_state->status == DS_OK && !h_state->want_grow) {
-            set_last_error("a batch made no progress");
-            return B200BPE_ERR_INTERNAL;
+            // a batch of one or two iterations can be used up by an arg-max that only found its
+            // candidate list stale (the merge then follows in the next iteration)
+            if (!(h_state->need_scan && ++idle_batches <= 4)) {
+                set_last_error("a batch made no progress");
+                return B200BPE_ERR_INTERNAL;
+            }
+        } else {
+            idle_batches = 0;
         }
+        if (timed && incremental) {
+            // only the full scans of the table count as arg-max bytes; the other launches read a short candidate list
+            stats.argmax_bytes += (16ull << table_log2) * (uint64_t)(h_state->full_scans - full_scans_seen);
+        }
+        full_scans_seen = h_state->full_scans;
         merges_done = done_now;
         remaining -= got;
         cur_n = h_state->n[h_state->epoch & 1];
@@ -383,7 +416,7 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
         } else if (h_state->status != DS_OK) {
             return B200BPE_ERR_INTERNAL;
         }
-        if (cb) {
+        if (cb && (merges_done >= batch_target || early_stop || remaining == 0)) {
             b200bpe_progress p{};
             p.merge_index = merges_done;
             p.total_merges = merges_goal;
@@ -543,7 +576,7 @@ b200bpe_status b200bpe_trainer_pair_counts(b200bpe_trainer* h, uint64_t* keys_ou
         k_begin_batch<<<1, 1, 0, s>>>(t->d_state, 0xFFFFFFFFu);
         if (!as_is)
             k_pair_count<PC_SLOTS, PC_THREADS><<<t->grid_pc, PC_THREADS, PC_SMEM_BYTES, s>>>(
-                t->d_state, t->buf[0], t->buf[1], t->table);
+                t->d_state, t->buf[0], t->buf[1], t->table, t->d_log);
         PairSlot* tab = t->table;
         uint32_t tl2 = t->table_log2;
         if (t->ctx->world > 1) {

@@ -58,12 +58,25 @@ __device__ __forceinline__ void table_add(PairSlot* __restrict__ table, uint32_t
             if (k == 0ull) k = key;
         }
         if (k == key) {
-            atomicAdd(&table[slot].count, c);
+            const uint32_t old = atomicAdd(&table[slot].count, c);
+            // an increase that takes the count across the arg-max threshold puts the slot on the candidate list
+            if (c < 0x80000000u) {
+                const uint32_t tau = st->cand_tau;
+                if (old < tau && old + c >= tau) {
+                    const uint32_t i = atomicAdd(&st->cand_n, 1u);
+                    if (i < CAND_CAP) st->cand[i] = slot;
+                }
+            }
             return;
         }
         slot = (slot + 1) & mask;
     }
     atomicExch(&st->status, (uint32_t)DS_TABLE_FULL);
+}
+__device__ __forceinline__ void void_candidates(DevState* st) {
+    st->need_scan = 1u;
+    st->cand_tau = 0xFFFFFFFFu;
+    st->cand_n = 0u;
 }
 
 // Literal mode with an incrementally maintained table: k_merge_compact accounts for the merge as
@@ -145,25 +158,82 @@ __device__ __forceinline__ bool smem_count(uint32_t* __restrict__ skey, uint32_t
     return false;
 }
 
+__device__ __forceinline__ void warp_best(uint32_t& c, unsigned long long& k);
+__device__ __forceinline__ void void_candidates(DevState* st);
+__device__ __forceinline__ void setup_merge(DevState* st, const DevState* rd, uint32_t best_count,
+                                            unsigned long long best_key, uint32_t* __restrict__ log);
+
 template <int S, int THREADS>
 __global__ void __launch_bounds__(THREADS, PC_CTAS_PER_SM)
 k_pair_count(DevState* __restrict__ st, const uint32_t* __restrict__ buf0, const uint32_t* __restrict__ buf1,
-             PairSlot* table) {
+             PairSlot* table, uint32_t* __restrict__ log) {
     extern __shared__ __align__(16) unsigned char pc_smem[];
     uint32_t* skey = reinterpret_cast<uint32_t*>(pc_smem);
     uint32_t* scnt = skey + S;
 
-    // One thread reads the stop flags for the whole CTA: `status` can change while this kernel
-    // runs (another CTA may find the table full), and a CTA must not split at a barrier.
-    __shared__ uint32_t s_idle, s_tail;
+    // One copy of the control block per CTA (one 16-byte load per thread, one round trip), and one
+    // thread decides for the whole CTA: `status` can change while this kernel runs (another CTA may
+    // find the table full), and a CTA must not split at a barrier.
+    __shared__ __align__(16) DevState snap;
+    __shared__ uint32_t s_idle, s_tail, s_fuse, s_last;
+    __shared__ uint32_t r_c[THREADS / 32];
+    __shared__ unsigned long long r_k[THREADS / 32];
+    static_assert(sizeof(DevState) % 16 == 0 && sizeof(DevState) / 16 <= THREADS, "control block copy");
+    if (threadIdx.x < sizeof(DevState) / 16)
+        reinterpret_cast<uint4*>(&snap)[threadIdx.x] = __ldcg(reinterpret_cast<const uint4*>(st) + threadIdx.x);
+    __syncthreads();
     if (threadIdx.x == 0) {
-        s_idle = st->early_stop | st->target_hit | st->status | (st->incremental & (st->recount ^ 1u));
-        s_tail = st->tail_fix;
+        s_idle = snap.early_stop | snap.target_hit | snap.status | (snap.incremental & (snap.recount ^ 1u));
+        s_tail = snap.tail_fix;
+        // Nothing to count and a usable candidate list: the last CTA of this launch to finish can
+        // pick the next merge right here, and the arg-max kernel of this iteration has nothing to do.
+        s_fuse = (snap.incremental != 0u && snap.world == 1u && snap.recount == 0u && snap.need_scan == 0u &&
+                  snap.early_stop == 0u && snap.target_hit == 0u && snap.status == DS_OK) ? 1u : 0u;
     }
     __syncthreads();
     // literal mode, incremental table: finish the table update of the merge before this one
     if (s_tail) literal_tail_fix(st, buf0, buf1, table);
-    if (s_idle) return;
+    if (s_idle) {
+        if (!s_fuse) return;
+        __threadfence();   // this CTA's table updates and list entries are out before it is counted as done
+        __syncthreads();
+        if (threadIdx.x == 0) s_last = (atomicAdd(&st->k1_done, 1u) == gridDim.x - 1u) ? 1u : 0u;
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        PairSlot* tab = table ? table : snap.table;
+        const uint4* __restrict__ t4 = reinterpret_cast<const uint4*>(tab);
+        const uint32_t cand_n = __ldcg(&st->cand_n);   // the tail fix may have appended
+        const uint32_t n = min(cand_n, CAND_CAP);
+        uint32_t bc = 0u;
+        unsigned long long bk = 0ull;
+        for (uint32_t i = threadIdx.x; i < n; i += THREADS) {
+            const uint4 q = __ldcg(t4 + __ldcg(snap.cand + i));
+            const unsigned long long key = ((unsigned long long)q.y << 32) | q.x;
+            if (key != 0ull && is_better(q.z, key, bc, bk)) { bc = q.z; bk = key; }
+        }
+        warp_best(bc, bk);
+        if ((threadIdx.x & 31) == 0) { r_c[threadIdx.x >> 5] = bc; r_k[threadIdx.x >> 5] = bk; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w = 1; w < THREADS / 32; w++)
+                if (is_better(r_c[w], r_k[w], bc, bk)) { bc = r_c[w]; bk = r_k[w]; }
+            st->k1_done = 0u;
+            snap.status = __ldcg(&st->status);   // the tail fix may have found the table full
+            // The list decides as long as its best count is at least its threshold: everything
+            // else was below the threshold at the last full scan and has not crossed it since.
+            if (bc >= snap.cand_tau && cand_n < CAND_CAP && snap.since_scan < CAND_MAX_AGE) {
+                st->since_scan = snap.since_scan + 1u;
+                setup_merge(st, &snap, bc, bk, log);
+                st->presetup = 1u;
+            } else {
+                // the arg-max kernel of this iteration scans the table
+                void_candidates(st);
+                st->cand_tau_next = max(2u, min(snap.cand_tau, snap.cand_tau_next) / 2u);
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < 2 * S; i += THREADS) skey[i] = 0u;
     __syncthreads();
     const uint32_t e = st->epoch;
@@ -252,29 +322,39 @@ __device__ __forceinline__ void warp_best(uint32_t& c, unsigned long long& k) {
 }
 
 // The merge set-up of the reference (train.wgsl:340-364) plus this library's batch control.
-__device__ __forceinline__ void setup_merge(DevState* st, uint32_t best_count, unsigned long long best_key,
-                                            uint32_t* __restrict__ log) {
+// `rd` is where the current values are read from: the control block itself, or a copy of it that
+// the caller took at the start of its kernel (one load instead of a chain of dependent ones; no
+// field read here is written by anybody else while the arg-max kernel runs).
+__device__ __forceinline__ void setup_merge(DevState* st, const DevState* rd, uint32_t best_count,
+                                            unsigned long long best_key, uint32_t* __restrict__ log) {
     st->tail_fix = 0u;
-    if (st->status != DS_OK) { st->active = 0u; st->recount = 1u; return; }
-    if (best_count < 2u || st->next_id > TOKEN_MASK) {
+    if (rd->status != DS_OK) { st->active = 0u; st->recount = 1u; void_candidates(st); return; }
+    const uint32_t next_id = rd->next_id;
+    if (best_count < 2u || next_id > TOKEN_MASK) {
         st->early_stop = 1u;
         st->active = 0u;
         return;
     }
     const uint32_t a = (uint32_t)(best_key >> 32), b = (uint32_t)best_key;
-    st->a = a; st->b = b; st->max_count = best_count; st->new_id = st->next_id;
-    const uint32_t md = st->merges_done;
-    log[md * 4 + 0] = a; log[md * 4 + 1] = b; log[md * 4 + 2] = st->next_id; log[md * 4 + 3] = best_count;
-    st->next_id += 1u;
+    st->a = a; st->b = b; st->max_count = best_count; st->new_id = next_id;
+    const uint32_t md = rd->merges_done;
+    log[md * 4 + 0] = a; log[md * 4 + 1] = b; log[md * 4 + 2] = next_id; log[md * 4 + 3] = best_count;
+    st->next_id = next_id + 1u;
     st->merges_done = md + 1u;
-    if (md + 1u >= st->merges_target) st->target_hit = 1u;
-    st->k3_epoch = st->epoch;
+    if (md + 1u >= rd->merges_target) st->target_hit = 1u;
+    st->k3_epoch = rd->epoch;
     st->ticket = 0u;
     st->active = 1u;
     // Incremental table: a merge of two equal symbols collapses whole runs, which the local
     // update rule does not cover; the table is emptied and rebuilt by a full count instead.
-    st->recount = st->incremental ? (a == b ? 1u : 0u) : 1u;
-    st->tail_fix = (st->incremental && st->literal && a != b) ? 1u : 0u;
+    const uint32_t recount = rd->incremental ? (a == b ? 1u : 0u) : 1u;
+    st->recount = recount;
+    if (recount) void_candidates(st);   // the table is about to be rebuilt
+    st->tail_fix = (rd->incremental && rd->literal && a != b) ? 1u : 0u;
+}
+__device__ __forceinline__ void setup_merge(DevState* st, uint32_t best_count, unsigned long long best_key,
+                                            uint32_t* __restrict__ log) {
+    setup_merge(st, st, best_count, best_key, log);
 }
 
 // mode 0: single GPU — finish with setup_merge.
@@ -287,20 +367,70 @@ k_argmax_setup(DevState* __restrict__ st, PairSlot* table, CtaBest* __restrict__
     __shared__ unsigned long long sk[AM_THREADS / 32];
     __shared__ uint32_t socc[AM_THREADS / 32];
     __shared__ bool is_last;
-    // Neither flag changes before every CTA has passed this test: only the last CTA to finish
-    // writes them.  Once the run has stopped, nothing is left for the merge kernel to apply.
-    if (st->early_stop | st->target_hit) {
+    // One 16-byte load per thread copies the control block into shared memory: everything the
+    // kernel needs to know arrives in one round trip instead of a chain of dependent loads.
+    // Nothing in it changes before every CTA has taken its copy: only the last CTA to finish
+    // (or the one CTA of a candidate-list pass) writes the block.
+    __shared__ __align__(16) DevState snap;
+    static_assert(sizeof(DevState) % 16 == 0 && sizeof(DevState) / 16 <= AM_THREADS, "control block copy");
+    if (threadIdx.x < sizeof(DevState) / 16)
+        reinterpret_cast<uint4*>(&snap)[threadIdx.x] = __ldcg(reinterpret_cast<const uint4*>(st) + threadIdx.x);
+    __syncthreads();
+    // The count kernel of this iteration has already chosen the merge from the candidate list.
+    if (snap.presetup) {
+        if (blockIdx.x == 0 && threadIdx.x == 0) st->presetup = 0u;
+        return;
+    }
+    // Once the run has stopped, nothing is left for the merge kernel to apply.
+    if (snap.early_stop | snap.target_hit) {
         if (blockIdx.x == 0 && threadIdx.x == 0) { st->active = 0u; st->tail_fix = 0u; }
         return;
     }
-    const uint32_t C = 1u << st->table_log2;
-    const bool clear = st->incremental == 0u;  // an incrementally maintained table is never wiped here
-    if (table == nullptr) table = st->table;
+    const uint32_t C = 1u << snap.table_log2;
+    const bool clear = snap.incremental == 0u;  // an incrementally maintained table is never wiped here
+    if (table == nullptr) table = snap.table;
     uint4* __restrict__ t4 = reinterpret_cast<uint4*>(table);
     uint32_t bc = 0, occ = 0;
     unsigned long long bk = 0ull;
-    // four independent 16-byte loads in flight per thread: the scan is latency-bound otherwise
     const uint32_t stride = gridDim.x * AM_THREADS;
+    // Incremental table, single GPU: most merges only look at the candidate list.  `need_scan`,
+    // like the stop flags, is written by the last CTA to finish (or between kernels) only.
+    const bool listed = mode == 0 && snap.incremental != 0u;
+    const bool use_list = listed && snap.need_scan == 0u;
+    const uint32_t tau_scan = listed ? snap.cand_tau_next : 0xFFFFFFFFu;   // threshold of the list a full scan builds
+    uint32_t* __restrict__ cand = snap.cand;
+    if (use_list) {
+        // one CTA is enough for a list of at most a few thousand slots, and it needs no second phase
+        if (blockIdx.x != 0) return;
+        const uint32_t n = min(snap.cand_n, CAND_CAP);
+        for (uint32_t i = threadIdx.x; i < n; i += AM_THREADS) {
+            const uint4 q = __ldcg(t4 + cand[i]);
+            const unsigned long long key = ((unsigned long long)q.y << 32) | q.x;
+            if (key != 0ull && is_better(q.z, key, bc, bk)) { bc = q.z; bk = key; }
+        }
+        warp_best(bc, bk);
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        if (lane == 0) { sc[warp] = bc; sk[warp] = bk; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w = 1; w < AM_THREADS / 32; w++)
+                if (is_better(sc[w], sk[w], bc, bk)) { bc = sc[w]; bk = sk[w]; }
+            // The list decides as long as its best count is at least its threshold: everything
+            // else was below the threshold at the last full scan and has not crossed it since.
+            if (bc >= snap.cand_tau && snap.cand_n < CAND_CAP && snap.since_scan < CAND_MAX_AGE) {
+                st->since_scan = snap.since_scan + 1u;
+                setup_merge(st, &snap, bc, bk, log);
+            } else {
+                // no merge in this iteration; the next arg-max scans the table
+                void_candidates(st);
+                st->cand_tau_next = max(2u, min(snap.cand_tau, snap.cand_tau_next) / 2u);
+                st->active = 0u;
+                st->tail_fix = 0u;
+            }
+        }
+        return;
+    }
+    // four independent 16-byte loads in flight per thread: the scan is latency-bound otherwise
     for (uint32_t i0 = blockIdx.x * AM_THREADS + threadIdx.x; i0 < C; i0 += 4u * stride) {
         uint4 q[4];
 #pragma unroll
@@ -314,6 +444,10 @@ k_argmax_setup(DevState* __restrict__ st, PairSlot* table, CtaBest* __restrict__
             if (key != 0ull) {
                 occ++;
                 if (is_better(q[u].z, key, bc, bk)) { bc = q[u].z; bk = key; }
+                if (q[u].z >= tau_scan) {
+                    const uint32_t k = atomicAdd(&st->cand_n, 1u);
+                    if (k < CAND_CAP) cand[k] = i0 + u * stride;
+                }
                 if (clear) __stcg(t4 + i0 + u * stride, make_uint4(0u, 0u, 0u, 0u));
             }
         }
@@ -365,6 +499,20 @@ k_argmax_setup(DevState* __restrict__ st, PairSlot* table, CtaBest* __restrict__
         st->occupied = occ;
         if ((unsigned long long)occ * 2ull > (unsigned long long)C) st->want_grow = 1u;
         if (mode == 0) {
+            if (listed) {
+                st->full_scans += 1u;
+                st->since_scan = 0u;
+                if (tau_scan == 0xFFFFFFFFu || st->cand_n >= CAND_CAP) {
+                    // no usable list yet (first scan, or too many slots above the threshold): scan again next time
+                    const uint32_t over = st->cand_n >= CAND_CAP ? 1u : 0u;
+                    void_candidates(st);
+                    st->cand_tau_next = over ? min(0x7FFFFFFFu, tau_scan) * 2u : max(2u, bc / 2u);
+                } else {
+                    st->need_scan = 0u;
+                    st->cand_tau = tau_scan;
+                    st->cand_tau_next = max(2u, bc / 2u);
+                }
+            }
             setup_merge(st, bc, bk, log);
         } else {
             const uint32_t pair32 = ((uint32_t)(bk >> 32) << 16) | ((uint32_t)bk & 0xFFFFu);
