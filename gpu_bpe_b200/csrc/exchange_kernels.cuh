@@ -4,7 +4,8 @@
 // at word starts into one contiguous span per GPU (pairs never cross a word start, so local
 // counting and local merging stay exact).  Per merge:
 //
-//   1. k_partition    each rank empties its local table into one outgoing bucket per owner,
+//   1. k_partition    each rank copies its local table (kept up to date by its merge kernel, or
+//                     just counted and then emptied here) into one outgoing bucket per owner,
 //                     owner = hash(pair) mod world
 //   2. all-to-all     fixed-size NCCL send/recv of the buckets (slot 0 of a bucket is a header
 //                     holding its fill, so buckets never need clearing)
@@ -32,11 +33,12 @@ k_partition(DevState* __restrict__ st, PairSlot* __restrict__ table, PairSlot* _
             uint32_t* __restrict__ fill, uint32_t cap, uint32_t world) {
     if (st->early_stop | st->target_hit) return;
     const uint32_t C = 1u << st->table_log2;
+    const bool keep = st->incremental != 0u;   // an incrementally maintained table stays as it is (dead keys are skipped)
     uint4* __restrict__ t4 = reinterpret_cast<uint4*>(table);
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < C; i += gridDim.x * blockDim.x) {
         const uint4 q = __ldcg(t4 + i);
         const unsigned long long key = ((unsigned long long)q.y << 32) | q.x;
-        if (key != 0ull) {
+        if (key != 0ull && !(keep && q.z == 0u)) {
             const uint32_t o = owner_of(hash_pair(key), world);
             const uint32_t d = atomicAdd(&fill[o], 1u) + 1u;  // slot 0 is the header
             if (d < cap) {
@@ -44,7 +46,7 @@ k_partition(DevState* __restrict__ st, PairSlot* __restrict__ table, PairSlot* _
             } else {
                 atomicCAS(&st->status, (uint32_t)DS_OK, (uint32_t)DS_BUCKET_FULL);
             }
-            __stcg(t4 + i, make_uint4(0u, 0u, 0u, 0u));
+            if (!keep) __stcg(t4 + i, make_uint4(0u, 0u, 0u, 0u));
         }
     }
 }

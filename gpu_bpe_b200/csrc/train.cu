@@ -37,7 +37,7 @@ struct Trainer {
     uint32_t* d_sym_init = nullptr;
     bool own_inputs = true;
     bool has_mask = false;
-    bool incremental = false;  // table updated in place by the merge kernel (single GPU, unless FULL_RECOUNT)
+    bool incremental = false;  // local table updated in place by the merge kernel (unless FULL_RECOUNT)
     // working set
     uint32_t* buf[2] = {nullptr, nullptr};
     uint64_t cap_elems = 0;
@@ -470,7 +470,7 @@ static b200bpe_status make_trainer(b200bpe_ctx* c, const uint8_t* bytes, const u
     b200bpe_status r = check_opts(&c->c, opts, &t->opts);
     if (r) { delete t; return r; }
     t->merges_goal = t->opts.target_vocab_size - t->opts.first_token_id;
-    t->incremental = c->c.world == 1 && !(t->opts.flags & B200BPE_FLAG_FULL_RECOUNT);
+    t->incremental = !(t->opts.flags & B200BPE_FLAG_FULL_RECOUNT);
     auto fail = [&](b200bpe_status st) { delete t; return st; };
     cudaStream_t s = c->c.stream;
     const size_t nb = std::max<uint64_t>(n, 1);

@@ -387,7 +387,7 @@ k_argmax_setup(DevState* __restrict__ st, PairSlot* table, CtaBest* __restrict__
         return;
     }
     const uint32_t C = 1u << snap.table_log2;
-    const bool clear = snap.incremental == 0u;  // an incrementally maintained table is never wiped here
+    const bool clear = snap.incremental == 0u || mode == 1;  // an incrementally maintained table is never wiped here; a table of owned pairs always is
     if (table == nullptr) table = snap.table;
     uint4* __restrict__ t4 = reinterpret_cast<uint4*>(table);
     uint32_t bc = 0, occ = 0;
