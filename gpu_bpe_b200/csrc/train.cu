@@ -112,7 +112,7 @@ b200bpe_status Trainer::alloc_common() {
     grid_pc = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)sms * PC_CTAS_PER_SM, (nvec + PC_THREADS - 1) / PC_THREADS));
     grid_am = std::max(1, std::min(sms * 4, (int)((1u << table_log2) / (AM_THREADS * 4))));
     const uint64_t ntiles = (n0 + MC_TILE - 1) / MC_TILE;
-    grid_mc = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)sms * 3, ntiles));
+    grid_mc = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)sms * 4, ntiles));
     B2_CUDA(cudaMalloc(&d_cta_best, sizeof(CtaBest) * (size_t)(sms * 4 + 1)));
     B2_CUDA(cudaMalloc(&d_cand, sizeof(uint32_t) * CAND_CAP));
     B2_CUDA(cudaMalloc(&d_desc, sizeof(unsigned long long) * (ntiles + 1)));

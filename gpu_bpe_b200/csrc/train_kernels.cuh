@@ -27,8 +27,8 @@ constexpr int AM_THREADS = 256;
 constexpr int MC_THREADS = 256;
 constexpr int MC_ROWS = 4;                               // uint4 rows per thread per sub-tile
 constexpr int MC_SUB = MC_THREADS * 4 * MC_ROWS;         // 4,096 symbols per sub-tile
-constexpr int MC_SUBS = 4;                               // sub-tiles per tile
-constexpr int MC_TILE = MC_SUB * MC_SUBS;                // 16,384 symbols per tile: one look-back each
+constexpr int MC_SUBS = 3;                               // sub-tiles per tile (48 KB of shared memory: four CTAs per SM)
+constexpr int MC_TILE = MC_SUB * MC_SUBS;                // 12,288 symbols per tile: one look-back each
 constexpr int MC_SMEM_BYTES = (MC_TILE + 8) * 4;         // the tile and its edges (dynamic shared memory)
 constexpr int MC_WARPS = MC_THREADS / 32;
 constexpr uint32_t LOOKBACK_MAX_SPINS = 1u << 22;        // bounded wait; then DS_LOOKBACK_TIMEOUT
@@ -724,21 +724,25 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t pari
     return false;
 }
 
-// One tile = 16,384 symbols (64 KB).  One asynchronous bulk copy brings the whole tile into shared
-// memory; the tile is then worked through as four sub-tiles of 4,096 symbols: in a sub-tile warp w
-// owns the 512 consecutive symbols [w * 512, (w + 1) * 512) as four 16-byte rows per lane, so a
-// warp's kept symbols are contiguous in the output.  Per sub-tile: read the rows from shared
-// memory, decide per symbol (rewritten? dropped?), rank within the warp, barrier, and write the kept
-// symbols back into the SAME shared buffer at their tile-local rank (a rank never exceeds the
-// position it came from, and everything at or beyond the sub-tile's end is still untouched input).
-// Per tile: publish the kept count, look back for the tile's global offset (warp 0), copy the
-// compacted run out with 16-byte stores whatever the alignment of the destination, then start the
-// next tile's bulk copy.  Tiles are handed out by an atomic ticket so that a waiting tile's
-// predecessors are always running.
+// One tile = 12,288 symbols (48 KB; four CTAs of 256 threads fit an SM, which measured faster than three
+// CTAs with 64 KB tiles or five with 32 KB).  One asynchronous bulk copy brings the whole tile into shared
+// memory; the tile is then worked through as three sub-tiles of 4,096 symbols: in a sub-tile warp w
+// owns the 512 consecutive symbols [w * 512, (w + 1) * 512), a span, as four 16-byte rows per lane,
+// so a span's kept symbols are a contiguous run of the output.
+//   pass 1    nothing in the buffer is written, so every neighbour read sees the snapshot.  Per span:
+//             a candidate test (can any pair merge at all?), then, only where needed, the bit logic
+//             that decides every symbol (kept? rewritten?), the pair deltas, the in-place rewrite of
+//             the source (literal mode), and the span's kept count.  One barrier, then the tile's
+//             kept count is published, long before the tile needs its own offset.
+//   pass 2    every warp compacts its touched spans in place (a span belongs to one warp: no barrier).
+//   look-back the whole CTA inspects 256 earlier tiles per round for the tile's global offset.
+//   copy-out  every warp writes its spans with 16-byte stores whatever the alignment of the
+//             destination; then the next tile's bulk copy starts.
+// Tiles are handed out by an atomic ticket so that a waiting tile's predecessors are always running.
 //
-// Why one look-back per 64 KB: the tiles of a launch move in waves, a wave resolves its offsets
-// front to back at one look-back window (32 tiles) per L2 round trip, and that chain, not HBM,
-// bounds the kernel when a tile is small.
+// Why one look-back per 48 KB: the tiles of a launch move in waves, a wave resolves its offsets
+// front to back at one look-back round per L2 round trip, and that chain, not HBM, bounds the
+// kernel when a tile is small.
 //
 // Neighbours across rows, sub-tiles and tiles are read from the shared buffer: the symbol before
 // the tile sits in front of it, the three after it behind it (plain loads).  Such a symbol may
@@ -761,7 +765,7 @@ __device__ unsigned long long g_phase_cycles[8];
 #endif
 
 template <bool LITERAL, bool INCR>
-__global__ void __launch_bounds__(MC_THREADS, 3)
+__global__ void __launch_bounds__(MC_THREADS, 4)
 k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsigned long long* __restrict__ desc,
                 PairSlot* table, DeltaQueues dq) {
     extern __shared__ __align__(16) uint32_t mc_smem[];  // 4 words (the last: left edge), the tile, 4 words (right edge)
@@ -985,7 +989,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
         // offsets of the spans within the tile's output, and the tile's kept count
         uint32_t span_off, span_cnt_reg, agg;
         {
-            const uint32_t c = span_cnt[lane];   // MC_SUBS * MC_WARPS == 32 spans, in tile order
+            const uint32_t c = lane < MC_SUBS * MC_WARPS ? span_cnt[lane] : 0u;   // the spans of the tile, in tile order
             span_cnt_reg = c;
             uint32_t incl = c;
 #pragma unroll
