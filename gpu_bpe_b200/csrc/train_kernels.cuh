@@ -21,6 +21,7 @@ constexpr int PC_THREADS = 1024;     // pair count: threads per CTA
 constexpr int PC_SLOTS = 12288;      // pair count: shared-memory slots per CTA (8 B each = 96 KB: two CTAs per SM)
 constexpr int PC_CTAS_PER_SM = 2;
 constexpr int PC_SMEM_BYTES = PC_SLOTS * 8;
+constexpr int PC_IDLE_CTAS = 64;     // pair count: CTAs that stay when there is nothing to count (literal tail fix, next merge)
 constexpr int PC_LOCAL_PROBES = 2;   // linear probes in shared memory before going to the global table
 constexpr int TABLE_MAX_PROBE = 1024;
 constexpr int AM_THREADS = 256;
@@ -46,9 +47,12 @@ __device__ __forceinline__ bool is_better(uint32_t cn, unsigned long long kn, ui
     return cn > co || (cn == co && kn < ko);
 }
 
-// Add `c` to the count of `key` in the global table (insert on first sight).
+// Add `c` to the count of `key` in the global table (insert on first sight).  `tau` is the
+// threshold of the arg-max candidate list (DevState.cand_tau, read once by the caller): an increase
+// that takes a count across it appends the slot to the list.  Decreases need no answer from the
+// atomic unit and are sent as reductions.
 __device__ __forceinline__ void table_add(PairSlot* __restrict__ table, uint32_t logC, unsigned long long key,
-                                          uint32_t h, uint32_t c, DevState* st) {
+                                          uint32_t h, uint32_t c, DevState* st, uint32_t tau) {
     const uint32_t mask = (1u << logC) - 1u;
     uint32_t slot = h >> (32 - logC);
     for (int p = 0; p < TABLE_MAX_PROBE; p++) {
@@ -58,10 +62,10 @@ __device__ __forceinline__ void table_add(PairSlot* __restrict__ table, uint32_t
             if (k == 0ull) k = key;
         }
         if (k == key) {
-            const uint32_t old = atomicAdd(&table[slot].count, c);
-            // an increase that takes the count across the arg-max threshold puts the slot on the candidate list
-            if (c < 0x80000000u) {
-                const uint32_t tau = st->cand_tau;
+            if (c >= 0x80000000u || tau == 0xFFFFFFFFu) {
+                atomicAdd(&table[slot].count, c);
+            } else {
+                const uint32_t old = atomicAdd(&table[slot].count, c);
                 if (old < tau && old + c >= tau) {
                     const uint32_t i = atomicAdd(&st->cand_n, 1u);
                     if (i < CAND_CAP) st->cand[i] = slot;
@@ -72,6 +76,10 @@ __device__ __forceinline__ void table_add(PairSlot* __restrict__ table, uint32_t
         slot = (slot + 1) & mask;
     }
     atomicExch(&st->status, (uint32_t)DS_TABLE_FULL);
+}
+__device__ __forceinline__ void table_add(PairSlot* __restrict__ table, uint32_t logC, unsigned long long key,
+                                          uint32_t h, uint32_t c, DevState* st) {
+    table_add(table, logC, key, h, c, st, c >= 0x80000000u ? 0xFFFFFFFFu : st->cand_tau);
 }
 __device__ __forceinline__ void void_candidates(DevState* st) {
     st->need_scan = 1u;
@@ -89,43 +97,53 @@ __device__ __forceinline__ void void_candidates(DevState* st) {
 // count kernel (which has nothing else to do while the table is maintained incrementally), or by
 // k_literal_tail at the end of a batch.  `tail_fix` is rewritten by the next set-up step, after
 // every caller of the grid has read it.
-__device__ __forceinline__ void literal_tail_fix(DevState* __restrict__ st, const uint32_t* buf0, const uint32_t* buf1,
-                                                 PairSlot* table) {
-    if (table == nullptr) table = st->table;
-    const uint32_t e = st->k3_epoch;   // the merge just applied; `epoch` is already one further
-    const uint32_t N = st->n[e & 1], N1 = st->n[(e + 1u) & 1u], V = st->v_kept;
+__device__ __forceinline__ void literal_tail_fix(DevState* __restrict__ st, const DevState* rd, const uint32_t* buf0,
+                                                 const uint32_t* buf1, PairSlot* table, uint32_t nblocks) {
+    // `rd`: the control block, or the caller's copy of it (nothing read here changes meanwhile)
+    if (table == nullptr) table = rd->table;
+    const uint32_t e = rd->k3_epoch;   // the merge just applied; `epoch` is already one further
+    const uint32_t N = rd->n[e & 1], N1 = rd->n[(e + 1u) & 1u], V = rd->v_kept;
     const uint32_t* __restrict__ src = (e & 1) ? buf1 : buf0;
     const uint32_t* __restrict__ dst = (e & 1) ? buf0 : buf1;
-    const uint32_t B = st->b, NW = st->new_id, limit = N - st->max_count;
-    const uint32_t logC = st->table_log2;
+    const uint32_t B = rd->b, NW = rd->new_id, limit = N - rd->max_count;
+    const uint32_t logC = rd->table_log2;
+    const uint32_t tau = rd->cand_tau;
     auto counted = [](uint32_t l, uint32_t r) { return !(r & WORD_START_BIT) && (l & TOKEN_MASK) != 0u && (r & TOKEN_MASK) != 0u; };
     auto emit = [&](uint32_t l, uint32_t r, uint32_t delta) {
         const unsigned long long key = ((unsigned long long)(l & TOKEN_MASK) << 32) | (r & TOKEN_MASK);
-        table_add(table, logC, key, hash_pair(key), delta, st);
+        table_add(table, logC, key, hash_pair(key), delta, st, tau);
     };
     // a position of the source is dropped iff its left neighbour was rewritten to the new symbol
-    auto dropped = [&](uint32_t i) { return i > 0u && i < N && (src[i - 1u] & TOKEN_MASK) == NW && !(src[i] & WORD_START_BIT) &&
-                                            (src[i] & TOKEN_MASK) == B; };
-    const uint32_t gtid = blockIdx.x * blockDim.x + threadIdx.x, gstride = gridDim.x * blockDim.x;
-    // (1) pairs whose left symbol is a kept source position >= limit: they were counted, but never copied
+    auto drops = [&](uint32_t left, uint32_t cur) { return (left & TOKEN_MASK) == NW && !(cur & WORD_START_BIT) && (cur & TOKEN_MASK) == B; };
+    const uint32_t gtid = blockIdx.x * blockDim.x + threadIdx.x, gstride = nblocks * blockDim.x;   // blocks 0..nblocks-1 take part
+    // (1) pairs whose left symbol is a kept source position >= limit: they were counted, but never
+    // copied.  The four symbols around a position are loaded together (one round trip).
     for (uint32_t i = limit + gtid; i < N; i += gstride) {
-        if (dropped(i)) continue;
-        const uint32_t r = (i + 1u < N && dropped(i + 1u)) ? i + 2u : i + 1u;
-        if (r < N && counted(src[i], src[r])) emit(src[i], src[r], 0xFFFFFFFFu);
+        const uint32_t sm = i > 0u ? __ldcg(src + i - 1u) : 0u, s0 = __ldcg(src + i);
+        const uint32_t s1 = i + 1u < N ? __ldcg(src + i + 1u) : 0u, s2 = i + 2u < N ? __ldcg(src + i + 2u) : 0u;
+        if (i > 0u && drops(sm, s0)) continue;
+        const bool d1 = i + 1u < N && drops(s0, s1);
+        const uint32_t r = d1 ? i + 2u : i + 1u, sr = d1 ? s2 : s1;
+        if (r < N && counted(s0, sr)) emit(s0, sr, 0xFFFFFFFFu);
     }
     // (2) the pair that joined the last copied symbol to the first kept source position >= limit
-    if (gtid == 0 && V > 0u) {
-        const uint32_t z0 = dropped(limit) ? limit + 1u : limit;
-        if (z0 < N && counted(dst[V - 1u], src[z0])) emit(dst[V - 1u], src[z0], 0xFFFFFFFFu);
+    if (gtid == 0 && V > 0u && limit < N) {
+        const uint32_t sm = limit > 0u ? __ldcg(src + limit - 1u) : 0u, s0 = __ldcg(src + limit);
+        const uint32_t s1 = limit + 1u < N ? __ldcg(src + limit + 1u) : 0u, last = __ldcg(dst + V - 1u);
+        const bool d0 = limit > 0u && drops(sm, s0);
+        const uint32_t z0 = d0 ? limit + 1u : limit, sz = d0 ? s1 : s0;
+        if (z0 < N && counted(last, sz)) emit(last, sz, 0xFFFFFFFFu);
     }
     // (3) the pairs of what the destination really holds from the last copied symbol on
-    for (uint32_t u = (V > 0u ? V - 1u : 0u) + gtid; u + 1u < N1; u += gstride)
-        if (counted(dst[u], dst[u + 1u])) emit(dst[u], dst[u + 1u], 1u);
+    for (uint32_t u = (V > 0u ? V - 1u : 0u) + gtid; u + 1u < N1; u += gstride) {
+        const uint32_t l = __ldcg(dst + u), r = __ldcg(dst + u + 1u);
+        if (counted(l, r)) emit(l, r, 1u);
+    }
 }
 
 __global__ void __launch_bounds__(256)
 k_literal_tail(DevState* __restrict__ st, const uint32_t* buf0, const uint32_t* buf1, PairSlot* table) {
-    if (st->tail_fix) literal_tail_fix(st, buf0, buf1, table);
+    if (st->tail_fix) literal_tail_fix(st, st, buf0, buf1, table, gridDim.x);
 }
 
 // ─────────────────────────────── pair count ───────────────────────────────
@@ -191,13 +209,17 @@ k_pair_count(DevState* __restrict__ st, const uint32_t* __restrict__ buf0, const
                   snap.early_stop == 0u && snap.target_hit == 0u && snap.status == DS_OK) ? 1u : 0u;
     }
     __syncthreads();
-    // literal mode, incremental table: finish the table update of the merge before this one
-    if (s_tail) literal_tail_fix(st, buf0, buf1, table);
+    // literal mode, incremental table: finish the table update of the merge before this one.  When
+    // there is nothing to count, a part of the grid is plenty for that (the tail is as long as the
+    // merged pair's count) and the other CTAs leave at once.
+    const uint32_t workers = s_idle ? min(gridDim.x, (uint32_t)PC_IDLE_CTAS) : gridDim.x;
+    if (blockIdx.x >= workers) return;
+    if (s_tail) literal_tail_fix(st, &snap, buf0, buf1, table, workers);
     if (s_idle) {
         if (!s_fuse) return;
         __threadfence();   // this CTA's table updates and list entries are out before it is counted as done
         __syncthreads();
-        if (threadIdx.x == 0) s_last = (atomicAdd(&st->k1_done, 1u) == gridDim.x - 1u) ? 1u : 0u;
+        if (threadIdx.x == 0) s_last = (atomicAdd(&st->k1_done, 1u) == workers - 1u) ? 1u : 0u;
         __syncthreads();
         if (!s_last) return;
         __threadfence();
@@ -678,6 +700,7 @@ __device__ __forceinline__ void apply_segment(DevState* st, DeltaQueues dq, cons
     const uint32_t nm = min(qcnt[0], dq.seg_cap), np = min(qcnt[1], dq.seg_cap);
     const uint32_t total = nm + np;
     if (total == 0u) return;
+    const uint32_t tau = st->cand_tau;
     const uint32_t* __restrict__ seg_m = dq.minus + (size_t)g * dq.seg_cap;
     const uint32_t* __restrict__ seg_p = dq.plus + (size_t)g * dq.seg_cap;
     for (uint32_t base = 0; base < total; base += blockDim.x) {
@@ -693,7 +716,7 @@ __device__ __forceinline__ void apply_segment(DevState* st, DeltaQueues dq, cons
             if (lane == __ffs(peers) - 1) {
                 const unsigned long long key = ((unsigned long long)(k32 >> 16) << 32) | (k32 & 0xFFFFu);
                 const uint32_t c = __popc(peers);
-                table_add(table, logC, key, hash_pair(key), neg ? (0u - c) : c, st);
+                table_add(table, logC, key, hash_pair(key), neg ? (0u - c) : c, st, tau);
             }
         }
     }

@@ -192,3 +192,21 @@ def test_incremental_with_frequent_equal_symbol_merges(engine):
         want = O.train(sym, 120, mode, threads=4)
         got = run_gpu(engine, sym, 120, mode)
         assert got[0] == want["merges"].tolist() and got[2] == want["symbols"].tolist()
+
+
+@pytest.mark.parametrize("mode", ["literal", "fixed"])
+def test_long_run_candidate_list_and_batch_ends(engine, mode):
+    """2,000 merges: the arg-max works from its candidate list, falls back to full scans when the
+    list goes stale (the best count halves several times over such a run), and every batch still
+    ends at a multiple of 128 merges."""
+    _, _, sym = small_text(2, 41, 1 << 20)
+    want = O.train(sym, 2000, mode, threads=8)
+    s = TrainerSession.from_symbols(engine, sym, target_vocab_size=256 + 2000, compat_mode=mode)
+    seen = []
+    m, c, early = s.run(0, lambda p: seen.append(p.merge_index))
+    final = s.symbols().copy()
+    s.destroy()
+    assert np.concatenate([m, c[:, None]], axis=1).tolist() == want["merges"].tolist()
+    assert final.tolist() == want["symbols"].tolist()
+    n = len(m)
+    assert seen == [k for k in range(128, n, 128)] + [n]
