@@ -4,6 +4,7 @@ The compute path is libb200bpe.so (hand-written CUDA for sm_100a, C ABI in inclu
 these modules are the host-side mirror of the reference's JavaScript classes.
 """
 from .engine import BPEEngine
+from .export import buildBin, exportBin, mergeFiles, parseBin, vocabJson
 from .pretokenizer import PreTokenizer
 from .tokenizer import TrieTokenizer
 from .trainer import BPETrainer, TrainerSession
@@ -11,4 +12,5 @@ from .trie import compileVocabToTrie, parseHeader, parseTrieBuffers
 from .vocab import Vocab, model_from_json, model_to_json
 
 __all__ = ["BPEEngine", "BPETrainer", "TrainerSession", "TrieTokenizer", "PreTokenizer", "Vocab", "compileVocabToTrie",
-           "parseHeader", "parseTrieBuffers", "model_to_json", "model_from_json"]
+           "parseHeader", "parseTrieBuffers", "model_to_json", "model_from_json", "mergeFiles", "vocabJson", "buildBin",
+           "parseBin", "exportBin"]

@@ -210,6 +210,16 @@ void b200bpe_tokenizer_destroy(b200bpe_tok*);
  * word_starts_out[n] gets 1 at the first byte of each word. */
 b200bpe_status b200bpe_pretokenize(const uint8_t* bytes, uint64_t n, uint8_t* word_starts_out);
 
+/* ── token file export: replaces the ".bin" writer of the Export tab (src/ui/export-controller.js:4,235-248) ──
+ * Host code.  Layout: u32 LE {0x44584654 'DXFT', vocabSize, tokenCount, vocabJsonBytes}, the tokens as u32 LE,
+ * then the vocabulary JSON {version, vocabSize, vocab, merges} (JSON.stringify form; may be empty). */
+b200bpe_status b200bpe_dxft_size(uint64_t n_tokens, uint64_t json_len, uint64_t* size_out);
+b200bpe_status b200bpe_dxft_write(const uint32_t* tokens, uint64_t n_tokens, uint32_t vocab_size, const void* json,
+                                  uint64_t json_len, void* out, uint64_t cap);
+/* fields_out = {magic, vocabSize, tokenCount, vocabJsonBytes}; B200BPE_ERR_BAD_TRIE_MAGIC / _TRUNCATED_TRIE on a bad file. */
+b200bpe_status b200bpe_dxft_parse(const void* buf, uint64_t len, uint32_t fields_out[4], uint64_t* tokens_offset,
+                                  uint64_t* json_offset);
+
 #ifdef __cplusplus
 }
 #endif

@@ -451,3 +451,28 @@ def tag_symbols(data: bytes, mask: bytes | None) -> list[int]:
     if mask is None:
         return word_boundary(list(data))
     return [b | (WORD_START_BIT if m else 0) for b, m in zip(data, mask)]
+
+
+# ── the Export tab's ".bin" file (src/ui/export-controller.js:4,191-202,224-248) ──
+DXFT_MAGIC = 0x44584654
+
+
+def merge_files(files) -> bytes:
+    """Files joined by two line feeds (export-controller.js:191-202)."""
+    return b"\n\n".join(bytes(f) for f in files)
+
+
+def vocab_json(model) -> bytes:
+    """JSON.stringify({version, vocabSize, vocab, merges}) (export-controller.js:224-233)."""
+    if model is None:
+        return b""
+    import json
+    return json.dumps({"version": 1, "vocabSize": model["vocabSize"], "vocab": model["vocab"], "merges": model["merges"]},
+                      separators=(",", ":"), ensure_ascii=False).encode("utf-8")
+
+
+def dxft_bytes(tokens, vocab_size: int, vocab_bytes: bytes = b"") -> bytes:
+    """[MAGIC, vocabSize, tokenCount, vocabBytesLen] as u32 LE, the tokens as u32 LE, the JSON (export-controller.js:235-248)."""
+    import struct
+    tokens = [int(t) for t in tokens]
+    return struct.pack("<4I", DXFT_MAGIC, vocab_size, len(tokens), len(vocab_bytes)) + struct.pack(f"<{len(tokens)}I", *tokens) + vocab_bytes
