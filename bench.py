@@ -162,7 +162,7 @@ def main():
     import torch
     import torch.distributed as dist
 
-    from gpu_bpe_b200 import BPEEngine, TrainerSession, TrieTokenizer, _lib, synth
+    from gpu_bpe_b200 import BPEEngine, PreTokenizer, TrainerSession, TrieTokenizer, _lib, synth
     from gpu_bpe_b200.sharding import document_cuts, word_aligned_cuts
     from gpu_bpe_b200.vocab import Vocab
 
@@ -352,6 +352,28 @@ def main():
                                "algorithmic_bytes": "L input bytes + 4 T token bytes (this rank)"}}
         tok.destroy()
 
+    # ── pre-tokeniser on the device (a "next" row beside the hot path): word starts of this rank's bytes ──
+    pretok = None
+    if not args.no_encode:
+        import ctypes as C
+        d_ws = torch.empty(hi - lo, dtype=torch.uint8, device="cuda")
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        pt_ms = []
+        for i in range(4):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            _lib.check(_lib.lib().b200bpe_pretokenize_device(engine.ctx, C.c_void_p(d_bytes.data_ptr()), hi - lo,
+                                                              C.c_void_p(d_ws.data_ptr())), "b200bpe_pretokenize_device")
+            pt_ms.append((time.perf_counter() - t0) * 1e3)   # the call synchronises before it returns
+        assert np.array_equal(d_ws.cpu().numpy(), my_mask), "device pre-tokeniser and host pre-tokeniser disagree"
+        sample = my_data[: 8 * MIB]
+        t0 = time.perf_counter()
+        PreTokenizer(normalize=False).preTokenizeBytes(sample)
+        host_s = time.perf_counter() - t0
+        pretok = {"device_GB_per_s": (hi - lo) / 1e9 / (min(pt_ms[1:]) / 1e3), "device_ms": min(pt_ms[1:]),
+                  "host_GB_per_s": sample.size / 1e9 / host_s, "host_sample": "first 8 MiB, one core",
+                  "checked": "word-start mask identical to the host pre-tokeniser on the whole corpus"}
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu, r = cpu_baseline_sample(data, mask, args.cpu_seconds, mode)
@@ -369,7 +391,7 @@ def main():
                        "l2": "inputs (256 MiB of symbols per buffer) exceed L2; a 256 MiB buffer is rewritten between steps",
                        "parallelism": "single GPU" if world == 1 else f"corpus cut at word starts over {world} GPUs"},
             "e2e": e2e, "gpu_launches": gpu_launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
-            "encode": encode,
+            "encode": encode, "pretokenize": pretok,
         }))
     if world > 1:
         dist.destroy_process_group()

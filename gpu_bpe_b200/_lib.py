@@ -87,6 +87,8 @@ SIGNATURES = {
     "b200bpe_tokenizer_last_ms": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "b200bpe_tokenizer_destroy": (None, [C.c_void_p]),
     "b200bpe_pretokenize": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_void_p]),
+    "b200bpe_pretokenize_device": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]),
+    "b200bpe_pretokenize_gpu": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]),
     "b200bpe_dxft_size": (C.c_int32, [C.c_uint64, C.c_uint64, u64p]),
     "b200bpe_dxft_write": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_uint32, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64]),
     "b200bpe_dxft_parse": (C.c_int32, [C.c_void_p, C.c_uint64, u32p, u64p, u64p]),

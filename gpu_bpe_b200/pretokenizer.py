@@ -14,8 +14,11 @@ from . import _lib
 
 
 class PreTokenizer:
-    def __init__(self, normalize: bool = True):
+    def __init__(self, normalize: bool = True, engine=None):
+        """engine: a BPEEngine → the boundary rules run on its GPU (well-formed UTF-8 only: other input
+        raises, and a PreTokenizer without an engine takes any bytes); None → the library's host code."""
         self.normalize = normalize
+        self.engine = engine
 
     def preTokenizeBytes(self, raw) -> dict:
         raw = bytes(raw) if not isinstance(raw, (bytes, bytearray, np.ndarray)) else raw
@@ -30,7 +33,14 @@ class PreTokenizer:
             except UnicodeDecodeError:
                 pass  # pre_tokenizer.mjs:466-469: on failure the raw bytes are used
         mask = np.zeros(arr.size, np.uint8)
-        _lib.check(_lib.lib().b200bpe_pretokenize(arr.ctypes.data, arr.size, mask.ctypes.data), "b200bpe_pretokenize")
+        if self.engine is not None:
+            st = _lib.lib().b200bpe_pretokenize_gpu(self.engine.ctx, arr.ctypes.data, arr.size, mask.ctypes.data)
+            if st == 1:
+                raise ValueError("the input is not well-formed UTF-8: the device pre-tokeniser refuses it "
+                                 "(a PreTokenizer without an engine takes any bytes)")
+            _lib.check(st, "b200bpe_pretokenize_gpu")
+        else:
+            _lib.check(_lib.lib().b200bpe_pretokenize(arr.ctypes.data, arr.size, mask.ctypes.data), "b200bpe_pretokenize")
         return {"bytes": arr, "wordStarts": mask}
 
     def preTokenize(self, text: str) -> dict:

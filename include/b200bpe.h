@@ -209,6 +209,12 @@ void b200bpe_tokenizer_destroy(b200bpe_tok*);
  * (the reference normalises with a closed-source WASM library first, pre_tokenizer.mjs:465).
  * word_starts_out[n] gets 1 at the first byte of each word. */
 b200bpe_status b200bpe_pretokenize(const uint8_t* bytes, uint64_t n, uint8_t* word_starts_out);
+/* The same rules on the GPU, for well-formed UTF-8 (the last character may be cut short); other input is
+ * refused with B200BPE_ERR_BAD_ARG and the host function above takes it.  _device: device pointers, _gpu: host
+ * buffers (upload, kernel, read-back).  One kernel, one pass; the three-digit split of digit runs is carried
+ * across tiles by a decoupled look-back scan. */
+b200bpe_status b200bpe_pretokenize_device(b200bpe_ctx*, const uint8_t* d_bytes, uint64_t n, uint8_t* d_word_starts_out);
+b200bpe_status b200bpe_pretokenize_gpu(b200bpe_ctx*, const uint8_t* bytes, uint64_t n, uint8_t* word_starts_out);
 
 /* ── token file export: replaces the ".bin" writer of the Export tab (src/ui/export-controller.js:4,235-248) ──
  * Host code.  Layout: u32 LE {0x44584654 'DXFT', vocabSize, tokenCount, vocabJsonBytes}, the tokens as u32 LE,
