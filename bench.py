@@ -227,8 +227,10 @@ def main():
     ms_per_step = float(np.mean(step_ms))
     value = n_merges / (ms_per_step / 1e3)
     batches = (n_merges + 127) // 128
-    kernels_per_merge = (4 if mode == "literal" else 3) if world == 1 else 11
-    gpu_launches = args.steps * (1 + batches * (1 + 128 * kernels_per_merge))
+    # per step: k_tag_symbols; per batch: k_begin_batch, the graph's 128 + 4 spare iterations of
+    # {k_pair_count, k_argmax_setup, k_merge_compact} (sharded: + 8 exchange kernels), and k_literal_tail in literal mode
+    kernels_per_iter = 3 if world == 1 else 11
+    gpu_launches = args.steps * (1 + batches * (1 + 132 * kernels_per_iter + (1 if mode == "literal" else 0)))
 
     # ── per-kernel device time: one more run with every kernel bracketed by CUDA events ──
     prof = TrainerSession.create(engine, d_bytes.data_ptr(), d_mask.data_ptr(), n=hi - lo, device_pointers=True,
