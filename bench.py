@@ -334,6 +334,8 @@ def main():
             _lib.check(st, "b200bpe_encode_batch")
             e_ms.append(max_over_ranks((time.perf_counter() - t0) * 1e3))
         assert int(toff_h[-1]) == ntok, "host-buffer encode and resident encode disagree on the token count"
+        assert torch.equal(pin_out[:ntok], d_tok[:ntok].cpu()), "host-buffer encode and resident encode disagree on the tokens"
+        assert np.array_equal(toff_h.astype(np.int64), d_toff.cpu().numpy()), "document token offsets disagree"
         e_ms = e_ms[1:]
         tot_tok = ntok
         if world > 1:

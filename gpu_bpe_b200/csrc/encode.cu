@@ -410,7 +410,10 @@ struct Tokenizer {
         cudaFree(d_counts); cudaFree(d_chunk_off); cudaFree(d_out); cudaFree(d_doc_off); cudaFree(d_chunk_base);
         cudaFree(d_tok_off); cudaFree(d_desc); cudaFree(d_ctl); cudaFree(d_total);
         if (h_total) cudaFreeHost(h_total);
+        if (h_slices) cudaFreeHost(h_slices);
         for (auto e : ev) if (e) cudaEventDestroy(e);
+        for (auto e : slice_ev) cudaEventDestroy(e);
+        if (s_read) cudaStreamDestroy(s_read);
     }
 
     template <typename T>
@@ -463,9 +466,14 @@ struct Tokenizer {
     }
 
     // Walk + scan/compact on device-resident inputs.  d_docs == nullptr → one buffer.
+    // h_dst / evs: where this launch's {total, error flag} and its three timing events go (default:
+    // the tokenizer's own), so that several launches can be in flight on the stream.
     b200bpe_status launch(const uint8_t* d_bytes, uint64_t n, const uint64_t* d_docs, uint32_t n_docs,
-                          uint32_t* d_tokens, uint64_t cap, uint64_t* d_tok_offsets) {
+                          uint32_t* d_tokens, uint64_t cap, uint64_t* d_tok_offsets, uint64_t* h_dst = nullptr,
+                          cudaEvent_t* evs = nullptr) {
         cudaStream_t s = ctx->stream;
+        uint64_t* hd = h_dst ? h_dst : h_total;
+        cudaEvent_t* ev = evs ? evs : this->ev;
         if (ck_d == 0) set_persisting_window(ctx, d_trans, trans_bytes);  // keep the transition table resident in L2
         const uint64_t max_chunks = (n + chunk - 1) / chunk + (d_docs ? n_docs : 0);
         b200bpe_status r = ensure_work(std::max<uint64_t>(1, max_chunks));
@@ -488,9 +496,29 @@ struct Tokenizer {
         B2_CUDA(cudaEventRecord(ev[2], s));
         if (d_docs && d_tok_offsets)
             k_doc_token_offsets<<<std::max(1u, std::min(1024u, (n_docs + 256) / 256)), 256, 0, s>>>(cb, d_chunk_off, n_docs, d_tok_offsets);
-        B2_CUDA(cudaMemcpyAsync(h_total, d_total, 8, cudaMemcpyDeviceToHost, s));
-        B2_CUDA(cudaMemcpyAsync(h_total + 1, d_ctl, 8, cudaMemcpyDeviceToHost, s));
+        B2_CUDA(cudaMemcpyAsync(hd, d_total, 8, cudaMemcpyDeviceToHost, s));
+        B2_CUDA(cudaMemcpyAsync(hd + 1, d_ctl, 8, cudaMemcpyDeviceToHost, s));
         B2_CUDA(cudaGetLastError());
+        return B200BPE_OK;
+    }
+
+    // Pipelined batches: a second stream for the read-back, per-slice pinned results and events.
+    cudaStream_t s_read = nullptr;
+    uint64_t* h_slices = nullptr; uint32_t slices_cap = 0;
+    std::vector<cudaEvent_t> slice_ev;   // four per slice: three timing events, one "slice done"
+    b200bpe_status ensure_slices(uint32_t n_slices) {
+        if (!s_read) B2_CUDA(cudaStreamCreateWithFlags(&s_read, cudaStreamNonBlocking));
+        if (n_slices > slices_cap) {
+            if (h_slices) cudaFreeHost(h_slices);
+            h_slices = nullptr;
+            B2_CUDA(cudaMallocHost(&h_slices, (size_t)n_slices * 16));
+            slices_cap = n_slices;
+        }
+        while (slice_ev.size() < (size_t)n_slices * 4) {
+            cudaEvent_t e = nullptr;
+            B2_CUDA(cudaEventCreate(&e));
+            slice_ev.push_back(e);
+        }
         return B200BPE_OK;
     }
 
@@ -786,6 +814,8 @@ b200bpe_status b200bpe_encode(b200bpe_tok* h, const uint8_t* bytes, uint64_t n, 
     return B200BPE_OK;
 }
 
+constexpr uint64_t BATCH_SLICE_BYTES = 32ull << 20;   // host batches above twice this are encoded slice by slice
+
 b200bpe_status b200bpe_encode_batch(b200bpe_tok* h, const uint8_t* bytes, const uint64_t* doc_offsets, uint32_t n_docs,
                                     uint32_t* tokens_out, uint64_t cap, uint64_t* tok_offsets_out) {
     if (!h || !doc_offsets || !tok_offsets_out) return B200BPE_ERR_BAD_ARG;
@@ -794,23 +824,81 @@ b200bpe_status b200bpe_encode_batch(b200bpe_tok* h, const uint8_t* bytes, const 
     cudaStream_t s = t->ctx->stream;
     const uint64_t n = doc_offsets[n_docs] - doc_offsets[0];
     for (uint32_t d = 0; d < n_docs; d++) if (doc_offsets[d + 1] < doc_offsets[d]) return B200BPE_ERR_BAD_ARG;
+    // Slices of whole documents, about BATCH_SLICE_BYTES each: the upload and the kernels of one slice
+    // run while the tokens of the slices before it travel back (documents are independent, so the
+    // result does not depend on the cut).
+    std::vector<uint32_t> cut{0};
+    uint64_t slice_bytes = BATCH_SLICE_BYTES;
+    if (const char* e = std::getenv("B200BPE_BATCH_SLICE_BYTES")) {   // tests use small slices
+        const unsigned long long v = std::strtoull(e, nullptr, 10);
+        if (v >= 1024) slice_bytes = v;
+    }
+    if (n > 2 * slice_bytes) {
+        uint64_t start = doc_offsets[0];
+        for (uint32_t d = 1; d < n_docs; d++)
+            if (doc_offsets[d] - start >= slice_bytes) { cut.push_back(d); start = doc_offsets[d]; }
+    }
+    cut.push_back(n_docs);
+    const uint32_t n_slices = (uint32_t)cut.size() - 1;
     b200bpe_status r;
     if ((r = t->ensure(&t->d_in, &t->in_cap, n + 16))) return r;
     if ((r = t->ensure(&t->d_out, &t->out_cap, std::max<uint64_t>(1, n)))) return r;
-    if ((r = t->ensure(&t->d_doc_off, &t->doc_off_cap, (uint64_t)n_docs + 1))) return r;
-    if ((r = t->ensure(&t->d_tok_off, &t->tok_off_cap, (uint64_t)n_docs + 1))) return r;
-    // offsets relative to the first document, so the device buffer starts at 0
-    std::vector<uint64_t> rel((size_t)n_docs + 1);
-    for (uint32_t d = 0; d <= n_docs; d++) rel[d] = doc_offsets[d] - doc_offsets[0];
-    if (n) B2_CUDA(cudaMemcpyAsync(t->d_in, bytes + doc_offsets[0], n, cudaMemcpyHostToDevice, s));
-    B2_CUDA(cudaMemcpyAsync(t->d_doc_off, rel.data(), ((size_t)n_docs + 1) * 8, cudaMemcpyHostToDevice, s));
-    if ((r = t->launch(t->d_in, n, t->d_doc_off, n_docs, t->d_out, t->out_cap, t->d_tok_off))) return r;
-    uint64_t got = 0;
-    if ((r = t->finish(t->out_cap, &got))) return r;
-    B2_CUDA(cudaMemcpyAsync(tok_offsets_out, t->d_tok_off, ((size_t)n_docs + 1) * 8, cudaMemcpyDeviceToHost, s));
-    if (got > cap || (!tokens_out && got)) { cudaStreamSynchronize(s); return B200BPE_ERR_CAPACITY; }
-    if (got) B2_CUDA(cudaMemcpyAsync(tokens_out, t->d_out, got * 4, cudaMemcpyDeviceToHost, s));
+    if ((r = t->ensure(&t->d_doc_off, &t->doc_off_cap, (uint64_t)n_docs + n_slices + 1))) return r;
+    if ((r = t->ensure(&t->d_tok_off, &t->tok_off_cap, (uint64_t)n_docs + n_slices + 1))) return r;
+    // document offsets relative to the first byte of their slice, one run of (docs + 1) entries per slice
+    std::vector<uint64_t> rel((size_t)n_docs + n_slices);
+    uint64_t max_chunks = 1;
+    uint32_t max_docs = 1;
+    for (uint32_t i = 0; i < n_slices; i++) {
+        const uint32_t d0 = cut[i], d1 = cut[i + 1];
+        for (uint32_t d = d0; d <= d1; d++) rel[(size_t)d + i] = doc_offsets[d] - doc_offsets[d0];
+        max_chunks = std::max<uint64_t>(max_chunks, (doc_offsets[d1] - doc_offsets[d0] + t->chunk - 1) / t->chunk + (d1 - d0));
+        max_docs = std::max(max_docs, d1 - d0);
+    }
+    // every buffer a slice needs exists before the first one starts (growing one synchronises the stream)
+    if ((r = t->ensure_work(max_chunks))) return r;
+    if ((r = t->ensure(&t->d_chunk_base, &t->chunk_base_cap, (uint64_t)max_docs + 1))) return r;
+    if ((r = t->ensure_slices(n_slices))) return r;
+    B2_CUDA(cudaMemcpyAsync(t->d_doc_off, rel.data(), rel.size() * 8, cudaMemcpyHostToDevice, s));
+    for (uint32_t i = 0; i < n_slices; i++) {
+        const uint32_t d0 = cut[i], d1 = cut[i + 1];
+        const uint64_t b0 = doc_offsets[d0] - doc_offsets[0], nb = doc_offsets[d1] - doc_offsets[d0];
+        if (nb) B2_CUDA(cudaMemcpyAsync(t->d_in + b0, bytes + doc_offsets[d0], nb, cudaMemcpyHostToDevice, s));
+        if ((r = t->launch(t->d_in + b0, nb, t->d_doc_off + d0 + i, d1 - d0, t->d_out + b0, std::max<uint64_t>(1, nb),
+                           t->d_tok_off + d0 + i, t->h_slices + 2 * (size_t)i, &t->slice_ev[4 * (size_t)i])))
+            return r;
+        B2_CUDA(cudaEventRecord(t->slice_ev[4 * (size_t)i + 3], s));
+    }
+    // read-back on the second stream, slice by slice, as each one finishes
+    uint64_t acc = 0;
+    b200bpe_status result = B200BPE_OK;
+    std::vector<uint64_t> base(n_slices, 0);
+    t->walk_ms = t->compact_ms = 0;
+    for (uint32_t i = 0; i < n_slices; i++) {
+        const uint32_t d0 = cut[i], d1 = cut[i + 1];
+        const uint64_t b0 = doc_offsets[d0] - doc_offsets[0];
+        B2_CUDA(cudaEventSynchronize(t->slice_ev[4 * (size_t)i + 3]));
+        float a = 0, b = 0;
+        cudaEventElapsedTime(&a, t->slice_ev[4 * (size_t)i], t->slice_ev[4 * (size_t)i + 1]);
+        cudaEventElapsedTime(&b, t->slice_ev[4 * (size_t)i + 1], t->slice_ev[4 * (size_t)i + 2]);
+        t->walk_ms += a; t->compact_ms += b;
+        const uint64_t got = t->h_slices[2 * (size_t)i];
+        if ((uint32_t)(t->h_slices[2 * (size_t)i + 1] >> 32) != 0u) result = B200BPE_ERR_LOOKBACK_TIMEOUT;
+        base[i] = acc;
+        if (result == B200BPE_OK && (acc + got > cap || (!tokens_out && got))) result = B200BPE_ERR_CAPACITY;
+        if (result == B200BPE_OK) {
+            if (got) B2_CUDA(cudaMemcpyAsync(tokens_out + acc, t->d_out + b0, got * 4, cudaMemcpyDeviceToHost, t->s_read));
+            B2_CUDA(cudaMemcpyAsync(tok_offsets_out + d0, t->d_tok_off + d0 + i, (size_t)(d1 - d0) * 8, cudaMemcpyDeviceToHost, t->s_read));
+        }
+        acc += got;
+    }
+    B2_CUDA(cudaStreamSynchronize(t->s_read));
     B2_CUDA(cudaStreamSynchronize(s));
+    if (result != B200BPE_OK) return result;
+    // token offsets were relative to their slice
+    for (uint32_t i = 1; i < n_slices; i++)
+        for (uint32_t d = cut[i]; d < cut[i + 1]; d++) tok_offsets_out[d] += base[i];
+    tok_offsets_out[n_docs] = acc;
     return B200BPE_OK;
 }
 

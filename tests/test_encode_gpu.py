@@ -149,3 +149,23 @@ def test_trie_sizes_pick_their_layout(engine, trie_layout, n_tokens, alphabet, w
     data[::97] = 255  # and bytes outside the alphabet
     assert tok.encodeBytes(data).tolist() == O.encode(data, trie, tok.chunkSize, threads=4).tolist()
     tok.destroy()
+
+
+def test_batch_in_slices_equals_one_pass(engine, trained, monkeypatch):
+    """Large host batches are encoded slice by slice with the read-back of one slice under the work of
+    the next; the cut must not show (here forced with small slices)."""
+    from gpu_bpe_b200 import synth
+    vocab, trie = trained
+    data, _, _ = small_text(2, 81, 1 << 20)
+    offs = synth.doc_offsets(9, data.size, 257, 1.2)
+    offs[17] = offs[16]          # an empty document
+    tok = TrieTokenizer(engine, trie, vocab)
+    monkeypatch.delenv("B200BPE_BATCH_SLICE_BYTES", raising=False)
+    toks1, toff1 = tok.encodeBatch(data, offs)
+    for slice_bytes in (4096, 65536, 300_000):
+        monkeypatch.setenv("B200BPE_BATCH_SLICE_BYTES", str(slice_bytes))
+        toks2, toff2 = tok.encodeBatch(data, offs)
+        assert np.array_equal(toks1, toks2) and np.array_equal(toff1, toff2), slice_bytes
+    assert toks1.tolist() == np.concatenate([O.encode(data[int(offs[d]):int(offs[d + 1])], trie, tok.chunkSize)
+                                             if offs[d + 1] > offs[d] else np.zeros(0, np.uint32) for d in range(257)]).tolist()
+    tok.destroy()
