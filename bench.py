@@ -230,7 +230,8 @@ def main():
     # per step: k_tag_symbols; per batch: k_begin_batch, the graph's 128 + 4 spare iterations of
     # {k_pair_count, k_argmax_setup, k_merge_compact} (sharded: + 8 exchange kernels), and k_literal_tail in literal mode
     kernels_per_iter = 3 if world == 1 else 11
-    gpu_launches = args.steps * (1 + batches * (1 + 132 * kernels_per_iter + (1 if mode == "literal" else 0)))
+    iters = 132 if world == 1 else 128   # sharded runs carry no spare iterations
+    gpu_launches = args.steps * (1 + batches * (1 + iters * kernels_per_iter + (1 if mode == "literal" else 0)))
 
     # ── per-kernel device time: one more run with every kernel bracketed by CUDA events ──
     prof = TrainerSession.create(engine, d_bytes.data_ptr(), d_mask.data_ptr(), n=hi - lo, device_pointers=True,

@@ -74,6 +74,8 @@ struct Trainer {
     // Kernel argument for the pair table: on one GPU the kernels take it from the control block, so a
     // captured graph survives the table being replaced; the sharded path passes pointers.
     PairSlot* ktable() const { return ctx->world > 1 ? table : nullptr; }
+    // only an arg-max that works from a candidate list can use up an iteration without a merge
+    uint32_t spare_iters() const { return (incremental && ctx->world == 1) ? 4u : 0u; }
     b200bpe_status run(uint32_t max_merges, uint32_t* merges_out, uint32_t* counts_out, uint32_t* n_out,
                        uint32_t* early_out, b200bpe_progress_cb cb, void* user);
 };
@@ -251,7 +253,7 @@ b200bpe_status Trainer::enqueue_merge(int iter, bool timed) {
     return B200BPE_OK;
 }
 
-constexpr uint32_t SPARE_ITERS = 4;   // iterations beyond the batch size, for arg-max passes that only void their candidate list
+constexpr uint32_t SPARE_ITERS = 4;   // most iterations beyond the batch size that a graph or a timed batch carries
 
 b200bpe_status Trainer::build_graph() {
     if (graph) { cudaGraphExecDestroy(graph); graph = nullptr; }
@@ -259,7 +261,7 @@ b200bpe_status Trainer::build_graph() {
     cudaGraph_t g = nullptr;
     B2_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
     b200bpe_status r = B200BPE_OK;
-    for (uint32_t i = 0; i < opts.batch_merges + SPARE_ITERS && r == B200BPE_OK; i++) r = enqueue_merge((int)i, false);
+    for (uint32_t i = 0; i < opts.batch_merges + spare_iters() && r == B200BPE_OK; i++) r = enqueue_merge((int)i, false);
     cudaError_t e = cudaStreamEndCapture(s, &g);
     if (r != B200BPE_OK) { if (g) cudaGraphDestroy(g); return r; }
     B2_CUDA(e);
@@ -325,7 +327,7 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
             if (!graph) { b200bpe_status r = build_graph(); if (r) return r; }
             B2_CUDA(cudaGraphLaunch(graph, s));
         } else {
-            for (uint32_t i = 0; i < batch + SPARE_ITERS; i++) { b200bpe_status r = enqueue_merge((int)i, timed); if (r) return r; }
+            for (uint32_t i = 0; i < batch + spare_iters(); i++) { b200bpe_status r = enqueue_merge((int)i, timed); if (r) return r; }
         }
         // literal mode, incremental table: inside a batch the next merge's count kernel finishes the
         // table update of a merge; the batch's last merge gets it here
@@ -341,7 +343,7 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
         const uint32_t got = done_now - before;
         if (timed) {
             uint64_t nk = cur_n;
-            for (uint32_t i = 0; i < batch + SPARE_ITERS; i++) {   // (an iteration without a merge shifts the attribution of the ones after it: statistics only)
+            for (uint32_t i = 0; i < batch + spare_iters(); i++) {   // (an iteration without a merge shifts the attribution of the ones after it: statistics only)
                 float ms = 0;
                 const size_t b = (size_t)i * 8;
                 const bool merged = i < got;
