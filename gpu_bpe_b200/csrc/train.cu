@@ -594,8 +594,12 @@ b200bpe_status b200bpe_trainer_pair_counts(b200bpe_trainer* h, uint64_t* keys_ou
         B2_CUDA(cudaMalloc(&dc, std::max<size_t>(4, (size_t)dcap * 4)));
         B2_CUDA(cudaMalloc(&dn, 4));
         B2_CUDA(cudaMemsetAsync(dn, 0, 4, s));
-        k_dump_table<<<t->ctx->sm_count * 4, 256, 0, s>>>(tab, 1u << tl2, dk, dc, dcap, dn, as_is ? 0 : 1);
-        if (tab != t->table) B2_CUDA(cudaMemsetAsync(t->table, 0, sizeof(PairSlot) << t->table_log2, s));
+        // A table of owned pairs is always left empty (the next merge sums into it again).  A local table
+        // that is up to date stays; one that was only counted for this call is emptied, because the
+        // rebuild that is still pending starts from an empty table.
+        const bool owned_table = tab != t->table;
+        k_dump_table<<<t->ctx->sm_count * 4, 256, 0, s>>>(tab, 1u << tl2, dk, dc, dcap, dn, (owned_table || !as_is) ? 1 : 0);
+        if (owned_table && !as_is) B2_CUDA(cudaMemsetAsync(t->table, 0, sizeof(PairSlot) << t->table_log2, s));
         uint32_t nd = 0;
         B2_CUDA(cudaMemcpyAsync(&nd, dn, 4, cudaMemcpyDeviceToHost, s));
         B2_CUDA(cudaMemcpyAsync(t->h_state, t->d_state, sizeof(DevState), cudaMemcpyDeviceToHost, s));

@@ -39,7 +39,15 @@ def main():
     mine = s.pair_counts()
     parts = [None] * world
     dist.all_gather_object(parts, mine)
-    m, c, early = s.run()
+    # first half, then the exchanged counts of the half-trained corpus (the local tables are kept up
+    # to date by the merge kernel by now and must survive being read), then the rest
+    m1, c1, _ = s.run(merges // 2)
+    mid_counts = s.pair_counts()
+    mid_syms = s.symbols().copy()
+    mids = [None] * world
+    dist.all_gather_object(mids, (mid_counts, mid_syms))
+    m2, c2, early = s.run()
+    m, c = np.concatenate([m1, m2]), np.concatenate([c1, c2])
     final = s.symbols().copy()
     finals = [None] * world
     dist.all_gather_object(finals, final)
@@ -71,6 +79,12 @@ def main():
                 assert k not in merged, "a pair is owned by two ranks"
                 merged[((k >> 32) << 16) | (k & 0xFFFF)] = v
         assert merged == O.pair_counts(sym), "exchanged pair counts differ from the oracle"
+        mid = {}
+        for cnts, _ in mids:
+            for k, v in cnts.items():
+                assert k not in mid, "a pair is owned by two ranks (mid-run)"
+                mid[((k >> 32) << 16) | (k & 0xFFFF)] = v
+        assert mid == O.pair_counts(np.concatenate([sy for _, sy in mids])), "mid-run exchanged pair counts differ from the oracle"
         trie = M.compile_vocab_to_trie(vocab)
         for r in range(world):
             t, to = enc[r]
