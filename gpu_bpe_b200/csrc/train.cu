@@ -134,6 +134,10 @@ b200bpe_status Trainer::alloc_common() {
     B2_CUDA(cudaEventCreate(&ev_run1));
     B2_CUDA(cudaFuncSetAttribute(k_pair_count<PC_SLOTS, PC_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  PC_SMEM_BYTES));
+    // The count and merge kernels need the largest shared-memory carve-out; the small kernels between them ask for
+    // the same one, so that the SMs are not reconfigured from launch to launch.
+    B2_CUDA(cudaFuncSetAttribute(k_argmax_setup, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    B2_CUDA(cudaFuncSetAttribute(k_literal_tail, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     B2_CUDA(cudaFuncSetAttribute(k_merge_compact<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_SMEM_BYTES));
     B2_CUDA(cudaFuncSetAttribute(k_merge_compact<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_SMEM_BYTES));
     B2_CUDA(cudaFuncSetAttribute(k_merge_compact<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_SMEM_BYTES));
