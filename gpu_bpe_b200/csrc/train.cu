@@ -101,7 +101,9 @@ b200bpe_status Trainer::alloc_common() {
     B2_CUDA(cudaMalloc(&buf[1], cap_elems * 4));
     table_log2 = opts.table_log2;
     // Start small (every merge scans the whole table for the arg-max); it doubles when half full.
-    if (table_log2 == 0) table_log2 = std::min<uint32_t>(21, std::max<uint32_t>(15, ceil_log2(n0 / 128 + 1)));
+    // (sharded: sized for the whole corpus, because the distinct pairs of a shard, and the pairs a rank owns, do not
+    // shrink in proportion to the shard; too small a start costs a chain of grow-and-recount restarts)
+    if (table_log2 == 0) table_log2 = std::min<uint32_t>(21, std::max<uint32_t>(15, ceil_log2(n0 * (uint64_t)ctx->world / 128 + 1)));
     table_log2 = std::min(table_log2, MAX_TABLE_LOG2);
     B2_CUDA(cudaMalloc(&table, sizeof(PairSlot) << table_log2));
     B2_CUDA(cudaMalloc(&d_state, sizeof(DevState)));
