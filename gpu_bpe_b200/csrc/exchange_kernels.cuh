@@ -35,12 +35,23 @@ k_partition(DevState* __restrict__ st, PairSlot* __restrict__ table, PairSlot* _
     const uint32_t C = 1u << st->table_log2;
     const bool keep = st->incremental != 0u;   // an incrementally maintained table stays as it is (dead keys are skipped)
     uint4* __restrict__ t4 = reinterpret_cast<uint4*>(table);
-    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < C; i += gridDim.x * blockDim.x) {
-        const uint4 q = __ldcg(t4 + i);
+    // A warp stays in the loop as a whole (the bound is tested on the warp's first slot).
+    // Room in a bucket is reserved once per warp and owner (match-any), not once per entry: the
+    // `world` fill counters would otherwise take one atomic for every live pair of the table.
+    const int lane = threadIdx.x & 31;
+    for (uint32_t i0 = blockIdx.x * blockDim.x + (threadIdx.x & ~31u); i0 < C; i0 += gridDim.x * blockDim.x) {
+        const uint32_t i = i0 + lane;
+        const uint4 q = i < C ? __ldcg(t4 + i) : make_uint4(0u, 0u, 0u, 0u);
         const unsigned long long key = ((unsigned long long)q.y << 32) | q.x;
-        if (key != 0ull && !(keep && q.z == 0u)) {
-            const uint32_t o = owner_of(hash_pair(key), world);
-            const uint32_t d = atomicAdd(&fill[o], 1u) + 1u;  // slot 0 is the header
+        const bool live = key != 0ull && !(keep && q.z == 0u);
+        const uint32_t o = live ? owner_of(hash_pair(key), world) : 0xFFFFFFFFu;
+        const uint32_t peers = __match_any_sync(0xFFFFFFFFu, o);
+        if (live) {
+            const int leader = __ffs(peers) - 1;
+            uint32_t base = 0u;
+            if (lane == leader) base = atomicAdd(&fill[o], (uint32_t)__popc(peers));
+            base = __shfl_sync(peers, base, leader);
+            const uint32_t d = base + (uint32_t)__popc(peers & ((1u << lane) - 1u)) + 1u;  // slot 0 is the header
             if (d < cap) {
                 reinterpret_cast<uint4*>(buckets)[(size_t)o * cap + d] = q;
             } else {
