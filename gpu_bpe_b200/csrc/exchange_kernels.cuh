@@ -85,7 +85,7 @@ k_accumulate(DevState* __restrict__ st, const PairSlot* __restrict__ inbox, uint
         for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < f; i += gridDim.x * blockDim.x) {
             const unsigned long long key = b[1 + i].key;
             const uint32_t c = b[1 + i].count;
-            if (key) table_add(owned, owned_log2, key, hash_pair(key) * 0x85EBCA6Bu, c, st);
+            if (key) table_add(owned, owned_log2, key, hash_pair(key) * 0x85EBCA6Bu, c, st, 0xFFFFFFFFu);  // no candidate list on owned tables
         }
     }
 }

@@ -317,7 +317,7 @@ k_pair_count(DevState* __restrict__ st, const uint32_t* __restrict__ buf0, const
                     const uint32_t peers = __match_any_sync(pend, keys[j]);
                     if (lane == __ffs(peers) - 1) {
                         const unsigned long long key = ((unsigned long long)(keys[j] >> 16) << 32) | (keys[j] & 0xFFFFu);
-                        table_add(table, logC, key, hash_pair(key), __popc(peers), st);
+                        table_add(table, logC, key, hash_pair(key), __popc(peers), st, snap.cand_tau);
                     }
                 }
             }
@@ -328,7 +328,7 @@ k_pair_count(DevState* __restrict__ st, const uint32_t* __restrict__ buf0, const
         const uint32_t k32 = skey[i];
         if (k32 != 0u) {
             const unsigned long long key = ((unsigned long long)(k32 >> 16) << 32) | (k32 & 0xFFFFu);
-            table_add(table, logC, key, hash_pair(key), scnt[i], st);
+            table_add(table, logC, key, hash_pair(key), scnt[i], st, snap.cand_tau);
         }
     }
 }
