@@ -366,8 +366,17 @@ k_scan_compact(const uint32_t* __restrict__ staging, const uint32_t* __restrict_
             if (cnt == 0u) continue;
             const uint64_t o = s_off[k];
             const uint32_t* __restrict__ src = staging + (tile * SC_THREADS + k) * (uint64_t)cs;
-            for (uint32_t i = lane; i < cnt; i += 32)
-                if (o + i < cap) out[o + i] = src[i];
+            // four loads in flight per lane before the first store: the copy is latency-bound otherwise
+            for (uint32_t i = lane; i < cnt; i += 128) {
+                const uint32_t v0 = src[i];
+                const uint32_t v1 = i + 32 < cnt ? src[i + 32] : 0u;
+                const uint32_t v2 = i + 64 < cnt ? src[i + 64] : 0u;
+                const uint32_t v3 = i + 96 < cnt ? src[i + 96] : 0u;
+                if (o + i < cap) out[o + i] = v0;
+                if (i + 32 < cnt && o + i + 32 < cap) out[o + i + 32] = v1;
+                if (i + 64 < cnt && o + i + 64 < cap) out[o + i + 64] = v2;
+                if (i + 96 < cnt && o + i + 96 < cap) out[o + i + 96] = v3;
+            }
         }
     }
 }
