@@ -142,6 +142,10 @@ struct Exchange {
         // What is sent per peer and merge is `cap` slots, sized to the traffic actually seen (the
         // host adapts it between batches from the all-reduced high-water mark), not to the table.
         cap = std::min<uint32_t>(cap_alloc, 32768u + 1u);
+        if (const char* e = std::getenv("B200BPE_EXCHANGE_CAP")) {   // tests start small to exercise the overflow path
+            const unsigned long v = std::strtoul(e, nullptr, 10);
+            if (v >= 2 && v <= cap_alloc) cap = (uint32_t)v;
+        }
         B2_CUDA(cudaMalloc(&send, sizeof(PairSlot) * (size_t)cap_alloc * world));
         B2_CUDA(cudaMalloc(&recv, sizeof(PairSlot) * (size_t)cap_alloc * world));
         B2_CUDA(cudaMalloc(&owned, sizeof(PairSlot) << owned_log2));

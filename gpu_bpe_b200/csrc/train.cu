@@ -410,7 +410,12 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
             if (over && xch.cap >= xch.cap_alloc) { h_state->status = DS_TABLE_FULL; }
             else if (xch.adapt(over, h_state->fill_hwm) || over) {
                 if (graph) { cudaGraphExecDestroy(graph); graph = nullptr; }
-                if (over) { k_clear_status<<<1, 1, 0, s>>>(d_state, table_log2, table); h_state->status = DS_OK; }
+                if (over) {
+                    // some pairs never reached their owners: count again, from an empty local table
+                    B2_CUDA(cudaMemsetAsync(table, 0, sizeof(PairSlot) << table_log2, s));
+                    k_clear_status<<<1, 1, 0, s>>>(d_state, table_log2, table);
+                    h_state->status = DS_OK;
+                }
             }
         }
         if (h_state->status == DS_TABLE_FULL || h_state->want_grow) {
@@ -613,6 +618,8 @@ b200bpe_status b200bpe_trainer_pair_counts(b200bpe_trainer* h, uint64_t* keys_ou
         if (t->h_state->status == DS_BUCKET_FULL) {
             // No all-reduce on this path, so the ranks cannot agree on a larger bucket here: give up.
             cudaFree(dk); cudaFree(dc); cudaFree(dn);
+            // the rebuild that k_clear_status asks for starts from an empty local table
+            B2_CUDA(cudaMemsetAsync(t->table, 0, sizeof(PairSlot) << t->table_log2, s));
             k_clear_status<<<1, 1, 0, s>>>(t->d_state, t->table_log2, t->table);
             return B200BPE_ERR_CAPACITY;
         }

@@ -36,13 +36,15 @@ def main():
 
     s = TrainerSession.create(engine, data[lo:hi], mask[lo:hi], target_vocab_size=256 + merges, compat_mode="fixed")
     # exchanged counts before any merge: the union of the ranks' owned partitions is the global histogram
-    mine = s.pair_counts()
+    # (with buckets forced far too small the one-shot count exchange gives up by design; the run resizes them)
+    tiny = "B200BPE_EXCHANGE_CAP" in os.environ
+    mine = {} if tiny else s.pair_counts()
     parts = [None] * world
     dist.all_gather_object(parts, mine)
     # first half, then the exchanged counts of the half-trained corpus (the local tables are kept up
     # to date by the merge kernel by now and must survive being read), then the rest
     m1, c1, _ = s.run(merges // 2)
-    mid_counts = s.pair_counts()
+    mid_counts = {} if tiny else s.pair_counts()
     mid_syms = s.symbols().copy()
     mids = [None] * world
     dist.all_gather_object(mids, (mid_counts, mid_syms))
@@ -78,13 +80,13 @@ def main():
             for k, v in p.items():
                 assert k not in merged, "a pair is owned by two ranks"
                 merged[((k >> 32) << 16) | (k & 0xFFFF)] = v
-        assert merged == O.pair_counts(sym), "exchanged pair counts differ from the oracle"
+        assert tiny or merged == O.pair_counts(sym), "exchanged pair counts differ from the oracle"
         mid = {}
         for cnts, _ in mids:
             for k, v in cnts.items():
                 assert k not in mid, "a pair is owned by two ranks (mid-run)"
                 mid[((k >> 32) << 16) | (k & 0xFFFF)] = v
-        assert mid == O.pair_counts(np.concatenate([sy for _, sy in mids])), "mid-run exchanged pair counts differ from the oracle"
+        assert tiny or mid == O.pair_counts(np.concatenate([sy for _, sy in mids])), "mid-run exchanged pair counts differ from the oracle"
         trie = M.compile_vocab_to_trie(vocab)
         for r in range(world):
             t, to = enc[r]

@@ -14,11 +14,15 @@ def _gpus():
     return _lib.lib().b200bpe_device_count()
 
 
-@pytest.mark.parametrize("world", [2])
-def test_sharded_training_and_encoding_match_oracle(world):
+@pytest.mark.parametrize("world,first_cap", [(2, None), (2, 1025)])
+def test_sharded_training_and_encoding_match_oracle(world, first_cap):
+    """first_cap: exchange buckets that start far too small, so the run goes through bucket overflow,
+    resizing and the recount that follows."""
     if _gpus() < world:
         pytest.skip(f"needs {world} GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    if first_cap:
+        env["B200BPE_EXCHANGE_CAP"] = str(first_cap)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", "29611", os.path.join(ROOT, "tests", "multi_gpu_worker.py")]
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
