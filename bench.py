@@ -380,11 +380,17 @@ def main():
                   "checked": "word-start mask identical to the host pre-tokeniser on the whole corpus"}
 
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
-        cpu, r = cpu_baseline_sample(data, mask, args.cpu_seconds, mode)
+    parity = None
+    if rank == 0 and not args.no_cpu:
+        # N = 1: the timed CPU baseline; N > 1: a shorter run of the same oracle, only as the checker
+        sample, r = cpu_baseline_sample(data, mask, args.cpu_seconds if world == 1 else min(args.cpu_seconds, 6.0), mode)
         k = int(r["merges"].shape[0])
         assert np.array_equal(r["merges"][:, :3], merges[:k]), "GPU merge list differs from the CPU oracle"
-        cpu["checked"] = f"first {k} merges bit-exact with the GPU run"
+        assert np.array_equal(r["merges"][:, 3], counts[:k]), "GPU pair counts differ from the CPU oracle"
+        parity = f"first {k} merges and their counts bit-exact with the CPU oracle"
+        if world == 1:
+            cpu = sample
+            cpu["checked"] = parity
 
     sess.destroy()
     if rank == 0:
@@ -396,7 +402,7 @@ def main():
                        "l2": "inputs (256 MiB of symbols per buffer) exceed L2; a 256 MiB buffer is rewritten between steps",
                        "parallelism": "single GPU" if world == 1 else f"corpus cut at word starts over {world} GPUs"},
             "e2e": e2e, "gpu_launches": gpu_launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
-            "encode": encode, "pretokenize": pretok,
+            "encode": encode, "pretokenize": pretok, "parity": parity,
         }))
     if world > 1:
         dist.destroy_process_group()
