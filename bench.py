@@ -119,9 +119,10 @@ def run_reference(args):
     if rank != 0:
         return
     data, mask = make_corpus()
+    mode = args.mode or ("literal" if args.gpus == 1 else "fixed")   # the mode the GPU arm runs at this N
     times, vals = [], []
     for i in range(args.warmup + args.steps):
-        base, r = cpu_baseline_sample(data, mask, args.ref_seconds, "literal")
+        base, r = cpu_baseline_sample(data, mask, args.ref_seconds, mode)
         if i >= args.warmup:
             times.append(r["seconds"] * 1e3)
             vals.append(base["value"])
@@ -131,7 +132,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": v, "unit": "merges/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": float(np.mean(times)) if times else None, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "note": "each step is a time-bounded sample of the merge loop on the host cores"},
+        "config": {"workload": WORKLOAD, "compat_mode": mode,
+                   "note": "each step is a time-bounded sample of the merge loop on the host cores"},
         "cpu_baseline": base,
         "e2e": {"value": v, "unit": "merges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
