@@ -90,10 +90,6 @@ k_accumulate(DevState* __restrict__ st, const PairSlot* __restrict__ inbox, uint
     }
 }
 
-// arg-max over the owned table reads st->table_log2; this tiny kernel swaps the value in and out
-// so that the same k_argmax_setup serves both the local and the owned table.
-__global__ void k_set_table_log2(DevState* st, uint32_t v) { st->table_log2 = v; }
-
 __global__ void k_pack_flags(DevState* __restrict__ st, unsigned long long* __restrict__ words) {
     const bool idle = (st->early_stop | st->target_hit) != 0u;
     words[0] = idle ? 0ull : st->best_packed;
@@ -212,9 +208,7 @@ struct Exchange {
         cudaStream_t s = ctx->stream;
         b200bpe_status r = enqueue_counts_only(ctx, st, table, table_log2);
         if (r) return r;
-        k_set_table_log2<<<1, 1, 0, s>>>(st, owned_log2);
-        k_argmax_setup<<<grid_am, AM_THREADS, 0, s>>>(st, owned, cta_best, log, 1);
-        k_set_table_log2<<<1, 1, 0, s>>>(st, table_log2);
+        k_argmax_setup<<<grid_am, AM_THREADS, 0, s>>>(st, owned, cta_best, log, 1, owned_log2);
         k_pack_flags<<<1, 1, 0, s>>>(st, words);
         int rc = ctx->nccl.AllReduce(words, words_max, 4, /*ncclUint64*/ 5, /*ncclMax*/ 2, ctx->comm, s);
         if (rc) return nccl_fail(ctx, rc, "ncclAllReduce");

@@ -239,7 +239,7 @@ b200bpe_status Trainer::enqueue_merge(int iter, bool timed) {
         B2_CUDA(ev(2));
     } else {
         B2_CUDA(ev(2));
-        k_argmax_setup<<<grid_am, AM_THREADS, 0, s>>>(d_state, ktable(), d_cta_best, d_log, 0);
+        k_argmax_setup<<<grid_am, AM_THREADS, 0, s>>>(d_state, ktable(), d_cta_best, d_log, 0, 0u);
     }
     B2_CUDA(ev(3));
     dsync("argmax_setup");

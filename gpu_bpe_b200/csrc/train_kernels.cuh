@@ -384,7 +384,7 @@ __device__ __forceinline__ void setup_merge(DevState* st, uint32_t best_count, u
 //         all-reduce (count << 32 | ~pair32); k_unpack_flags finishes after the collective.
 __global__ void __launch_bounds__(AM_THREADS)
 k_argmax_setup(DevState* __restrict__ st, PairSlot* table, CtaBest* __restrict__ cta_best,
-               uint32_t* __restrict__ log, int mode) {
+               uint32_t* __restrict__ log, int mode, uint32_t table_log2) {   // table_log2: 0 = the control block's
     __shared__ uint32_t sc[AM_THREADS / 32];
     __shared__ unsigned long long sk[AM_THREADS / 32];
     __shared__ uint32_t socc[AM_THREADS / 32];
@@ -408,7 +408,7 @@ k_argmax_setup(DevState* __restrict__ st, PairSlot* table, CtaBest* __restrict__
         if (blockIdx.x == 0 && threadIdx.x == 0) { st->active = 0u; st->tail_fix = 0u; }
         return;
     }
-    const uint32_t C = 1u << snap.table_log2;
+    const uint32_t C = 1u << (table_log2 ? table_log2 : snap.table_log2);
     const bool clear = snap.incremental == 0u || mode == 1;  // an incrementally maintained table is never wiped here; a table of owned pairs always is
     if (table == nullptr) table = snap.table;
     uint4* __restrict__ t4 = reinterpret_cast<uint4*>(table);
