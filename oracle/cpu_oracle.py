@@ -30,6 +30,14 @@ def lib():
         L.oracle_train.restype = C.c_int
         L.oracle_encode.argtypes = [u8p, C.c_uint64, u8p, C.c_uint64, C.c_uint32, C.c_int, u32p, C.c_uint64]
         L.oracle_encode.restype = C.c_uint64
+        L.word_oracle_train_symbols.argtypes = [u32p, C.c_uint64, C.c_uint32, C.c_uint32, C.c_int, u32p, u32p, u32p, u64p,
+                                                u64p, u64p]
+        L.word_oracle_train_symbols.restype = C.c_int
+        L.word_oracle_train_bytes.argtypes = [u8p, u8p, C.c_uint64, C.c_uint32, C.c_uint32, C.c_int, u32p, u32p, u32p,
+                                              u64p, u64p, u64p]
+        L.word_oracle_train_bytes.restype = C.c_int
+        L.oracle_replay_encode.argtypes = [u8p, C.c_uint64, u32p, C.c_uint32, u32p, C.c_uint64]
+        L.oracle_replay_encode.restype = C.c_uint64
         _lib = L
     return _lib
 
@@ -80,4 +88,40 @@ def encode(data: np.ndarray, trie: bytes, chunk_size: int, threads: int = 1) -> 
                             _p(out, C.c_uint32), cap)
     if n == 2**64 - 1:
         raise ValueError("bad trie")
+    return out[:n].copy()
+
+
+def train_words(sym_or_bytes: np.ndarray, max_merges: int, word_starts: np.ndarray | None = None, first_id: int = 256,
+                threads: int = 1):
+    """The "fixed"-mode merge loop on the dictionary of distinct words (oracle/word_oracle.cpp): the same
+    merge list as train(..., "fixed"), fast enough for full-size corpora.  Pass tagged u32 symbols, or u8
+    bytes with their word-start mask.  Returns dict(merges=(M,4) u32 [a,b,id,count], early_stop, n,
+    distinct_words, distinct_pairs)."""
+    merges = np.zeros((max(1, max_merges), 4), np.uint32)
+    nm, es = C.c_uint32(0), C.c_uint32(0)
+    fn, dw, dp = C.c_uint64(0), C.c_uint64(0), C.c_uint64(0)
+    if word_starts is None:
+        sym = np.ascontiguousarray(sym_or_bytes, dtype=np.uint32)
+        lib().word_oracle_train_symbols(_p(sym, C.c_uint32), sym.size, max_merges, first_id, threads,
+                                        _p(merges, C.c_uint32), C.byref(nm), C.byref(es), C.byref(fn), C.byref(dw),
+                                        C.byref(dp))
+    else:
+        b = np.ascontiguousarray(sym_or_bytes, dtype=np.uint8)
+        w = np.ascontiguousarray(word_starts, dtype=np.uint8)
+        assert b.size == w.size
+        lib().word_oracle_train_bytes(_p(b, C.c_uint8), _p(w, C.c_uint8), b.size, max_merges, first_id, threads,
+                                      _p(merges, C.c_uint32), C.byref(nm), C.byref(es), C.byref(fn), C.byref(dw),
+                                      C.byref(dp))
+    return dict(merges=merges[: nm.value].copy(), early_stop=bool(es.value), n=fn.value, distinct_words=dw.value,
+                distinct_pairs=dp.value)
+
+
+def replay_encode(data: np.ndarray, merges) -> np.ndarray:
+    """Merge-replay encoding (oracle/replay_oracle.cpp): merges = rows [a, b, new_id] in learned order."""
+    data = np.ascontiguousarray(data, dtype=np.uint8)
+    m = np.ascontiguousarray(np.asarray(merges, dtype=np.uint32).reshape(-1, 3)[:, :3] if len(merges) else
+                             np.zeros((0, 3), np.uint32))
+    out = np.empty(max(1, data.size), np.uint32)
+    n = lib().oracle_replay_encode(_p(data, C.c_uint8), data.size, _p(m, C.c_uint32), m.shape[0], _p(out, C.c_uint32),
+                                   out.size)
     return out[:n].copy()
