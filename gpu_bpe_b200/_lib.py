@@ -15,7 +15,7 @@ SYNTH_PATH = os.path.join(PKG, "libb200bpe_synth.so")
 u8p, u32p, u64p = C.POINTER(C.c_uint8), C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)
 
 COMPAT_LITERAL, COMPAT_FIXED = 0, 1
-FLAG_NO_GRAPH, FLAG_TIME_KERNELS, FLAG_FULL_RECOUNT = 1, 2, 4
+FLAG_NO_GRAPH, FLAG_TIME_KERNELS, FLAG_FULL_RECOUNT, FLAG_NCCL_EXCHANGE = 1, 2, 4, 8
 
 STATUS = {0: "OK", 1: "BAD_ARG", 2: "CUDA", 3: "NO_DEVICE", 4: "EMPTY_CORPUS", 5: "TABLE_FULL", 6: "LOOKBACK_TIMEOUT",
           7: "BAD_TRIE_MAGIC", 8: "BAD_TRIE_VERSION", 9: "TRUNCATED_TRIE", 10: "CAPACITY", 11: "NCCL", 12: "OOM",
@@ -25,7 +25,7 @@ STATUS = {0: "OK", 1: "BAD_ARG", 2: "CUDA", 3: "NO_DEVICE", 4: "EMPTY_CORPUS", 5
 class TrainOpts(C.Structure):
     _fields_ = [("struct_size", C.c_uint32), ("target_vocab_size", C.c_uint32), ("first_token_id", C.c_uint32),
                 ("batch_merges", C.c_uint32), ("compat_mode", C.c_uint32), ("table_log2", C.c_uint32),
-                ("flags", C.c_uint32), ("reserved", C.c_uint32)]
+                ("flags", C.c_uint32), ("exchange_cap", C.c_uint32)]
 
 
 class Progress(C.Structure):
@@ -71,6 +71,8 @@ SIGNATURES = {
     "b200bpe_trainer_kernel_stats": (C.c_int32, [C.c_void_p, C.POINTER(KernelStats)]),
     "b200bpe_trainer_last_run_ms": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double)]),
     "b200bpe_trainer_last_reset_ms": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double)]),
+    "b200bpe_trainer_launches": (C.c_int32, [C.c_void_p, u64p]),
+    "b200bpe_trainer_exchange_kind": (C.c_int32, [C.c_void_p, u32p]),
     "b200bpe_trainer_destroy": (None, [C.c_void_p]),
     "b200bpe_trie_compile": (C.c_int32, [C.c_void_p, u64p, C.c_uint32, C.c_void_p, C.POINTER(C.c_size_t)]),
     "b200bpe_trie_parse_header": (C.c_int32, [C.c_void_p, C.c_size_t, u32p]),

@@ -22,6 +22,7 @@ b200bpe_status load_nccl(const char* path, NcclApi* api) {
     B2_SYM(CommInitRank, "ncclCommInitRank")
     B2_SYM(CommDestroy, "ncclCommDestroy")
     B2_SYM(AllReduce, "ncclAllReduce")
+    B2_SYM(AllGather, "ncclAllGather")
     B2_SYM(Send, "ncclSend")
     B2_SYM(Recv, "ncclRecv")
     B2_SYM(GroupStart, "ncclGroupStart")

@@ -58,20 +58,34 @@ struct DevState {
     // Candidate list of the arg-max (incremental table only): the slots whose count was at least
     // cand_tau at the last full scan of the table, plus every slot whose count has crossed cand_tau
     // upwards since.  While the best listed count is >= cand_tau the list holds the global best.
-    uint32_t need_scan;     // the next arg-max must scan the whole table (and rebuild the list)
+    uint32_t scan_from;     // the arg-max scans the whole table (and rebuilds the list) in every iteration numbered >= this
     uint32_t cand_n;        // entries appended to the list (may exceed its capacity: then it is void)
     uint32_t cand_tau;      // threshold of the list; 0xFFFFFFFF = no list, nothing is appended
     uint32_t cand_tau_next; // threshold the next full scan will use
     uint32_t since_scan;    // merges since the last full scan
     uint32_t full_scans;    // full scans since creation/reset (statistics)
-    uint32_t k1_done;       // CTAs of the count kernel that have finished (when its last CTA picks the next merge)
+    uint32_t k1_done;       // CTAs of the count kernel that have arrived at its end (the last one picks the next merge)
     PairSlot* table;        // the pair table (kept here so that replacing it does not invalidate a captured graph)
     uint32_t* cand;         // the candidate list: slot indices
-    uint32_t presetup;      // the count kernel has already chosen and set up this iteration's merge: the arg-max kernel skips
-    uint32_t pad[3];
+    // Iteration number: advanced by the merge kernel (one thread, at its entry), so it is the same for
+    // every CTA of the count and arg-max kernels of an iteration whenever they read the block.  Flags
+    // that one CTA of those kernels sets for a LATER kernel are stored as iteration numbers, so a CTA
+    // that reads the block after that store still takes the same branch as the others.
+    uint32_t iter_no;
+    uint32_t presetup_at;   // iteration whose merge an earlier kernel of that iteration already chose and set up: its arg-max skips
+    // sharded runs with the peer-memory exchange
+    uint32_t xseq;          // sequence number of the next exchange round (the same on every rank)
+    uint32_t dlist_n;       // slots of the local delta table that hold an entry (appended on first insert)
+    uint32_t* dlist;        // their indices
+    PairSlot* owned;        // table of the pairs this rank owns, with their global counts
+    uint32_t owned_log2;
+    uint32_t owned_inserted; // keys inserted into the owned table since it was last emptied
+    uint32_t xdone[2];      // CTAs of the route / accumulate kernels that have arrived at their end
+    uint32_t pad[4];        // the block is copied as 16-byte words
 };
 constexpr uint32_t CAND_CAP = 1u << 13;      // entries of the candidate list (one CTA scans it)
 constexpr uint32_t CAND_MAX_AGE = 512;       // merges after which a full scan is due anyway (refreshes the table's fill)
+constexpr uint32_t SCAN_NEVER = 0xFFFFFFFFu; // DevState.scan_from: no full scan due
 
 struct CtaBest {
     unsigned long long key;

@@ -112,6 +112,19 @@ __global__ void k_unpack_flags(DevState* __restrict__ st, const unsigned long lo
     setup_merge(st, cnt, cnt ? key : 0ull, log);
 }
 
+// End of a batch: only the flags are taken over (no merge is set up).
+__global__ void k_unpack_status(DevState* __restrict__ st, const unsigned long long* __restrict__ words) {
+    if (words[1] > st->status) st->status = (uint32_t)words[1];
+    if (words[2]) st->want_grow = 1u;
+    if (words[3] > st->fill_hwm) st->fill_hwm = (uint32_t)words[3];
+}
+__global__ void k_pack_status(DevState* __restrict__ st, unsigned long long* __restrict__ words) {
+    words[0] = 0ull;
+    words[1] = st->status;
+    words[2] = st->want_grow;
+    words[3] = st->fill_hwm;
+}
+
 struct Exchange {
     PairSlot* send = nullptr;   // world buckets of `cap` slots
     PairSlot* recv = nullptr;   // world inboxes of `cap` slots
@@ -128,7 +141,8 @@ struct Exchange {
         send = recv = owned = nullptr; fill = nullptr; words = words_max = nullptr;
     }
 
-    b200bpe_status init(Ctx* ctx, uint32_t table_log2) {
+    // first_cap: bucket size to start with (0 = the default); tests start small to exercise the overflow path
+    b200bpe_status init(Ctx* ctx, uint32_t table_log2, uint32_t first_cap = 0) {
         const uint32_t world = (uint32_t)ctx->world;
         local_log2 = table_log2;
         owned_log2 = table_log2;
@@ -138,10 +152,7 @@ struct Exchange {
         // What is sent per peer and merge is `cap` slots, sized to the traffic actually seen (the
         // host adapts it between batches from the all-reduced high-water mark), not to the table.
         cap = std::min<uint32_t>(cap_alloc, 32768u + 1u);
-        if (const char* e = std::getenv("B200BPE_EXCHANGE_CAP")) {   // tests start small to exercise the overflow path
-            const unsigned long v = std::strtoul(e, nullptr, 10);
-            if (v >= 2 && v <= cap_alloc) cap = (uint32_t)v;
-        }
+        if (first_cap >= 2 && first_cap <= cap_alloc) cap = first_cap;
         B2_CUDA(cudaMalloc(&send, sizeof(PairSlot) * (size_t)cap_alloc * world));
         B2_CUDA(cudaMalloc(&recv, sizeof(PairSlot) * (size_t)cap_alloc * world));
         B2_CUDA(cudaMalloc(&owned, sizeof(PairSlot) << owned_log2));
@@ -155,9 +166,20 @@ struct Exchange {
         return B200BPE_OK;
     }
 
-    b200bpe_status resize(Ctx* ctx, uint32_t table_log2) {
+    b200bpe_status resize(Ctx* ctx, uint32_t table_log2, uint32_t first_cap = 0) {
         release();
-        return init(ctx, table_log2);
+        return init(ctx, table_log2, first_cap);
+    }
+
+    // After the last merge kernel of a batch: every rank takes the largest status and the other
+    // flags of the job, so that all ranks grow, resize or give up together.
+    b200bpe_status enqueue_status_sync(Ctx* ctx, DevState* st) {
+        cudaStream_t s = ctx->stream;
+        k_pack_status<<<1, 1, 0, s>>>(st, words);
+        int rc = ctx->nccl.AllReduce(words, words_max, 4, /*ncclUint64*/ 5, /*ncclMax*/ 2, ctx->comm, s);
+        if (rc) return nccl_fail(ctx, rc, "ncclAllReduce");
+        k_unpack_status<<<1, 1, 0, s>>>(st, words_max);
+        return B200BPE_OK;
     }
 
     // Between batches: fit the bucket size to the traffic.  Every rank sees the same all-reduced

@@ -11,6 +11,7 @@
 #include "ctx.cuh"
 #include "train_kernels.cuh"
 #include "exchange_kernels.cuh"
+#include "peer_exchange.cuh"
 
 namespace b200bpe {
 
@@ -25,6 +26,82 @@ uint32_t ceil_log2(uint64_t x) {
 }
 
 }  // namespace
+
+// Host side of the peer-memory exchange: this rank's exchange buffer (headers, best words, inboxes),
+// the peers' buffers mapped through CUDA IPC (one process per GPU), the table of owned pairs and
+// the list of delta-table slots to send.
+struct PeerExchange {
+    unsigned char* xbuf = nullptr;
+    size_t xbuf_bytes = 0;
+    PairSlot* owned = nullptr;
+    uint32_t owned_log2 = 0;
+    uint32_t* dlist = nullptr;
+    uint32_t* fill = nullptr;
+    void* mapped[PX_MAX_WORLD] = {};
+    PeerBufs pb{};
+    bool ok = false;
+
+    void release() {
+        for (auto& m : mapped) { if (m) cudaIpcCloseMemHandle(m); m = nullptr; }
+        cudaFree(xbuf); cudaFree(owned); cudaFree(dlist); cudaFree(fill);
+        xbuf = nullptr; owned = nullptr; dlist = nullptr; fill = nullptr;
+        ok = false;
+    }
+
+    // Collective over the job's ranks.  Returns OK with ok == false when some rank could not map its
+    // peers (every rank then takes the NCCL exchange instead).
+    b200bpe_status init(Ctx* ctx, uint32_t table_log2) {
+        const uint32_t world = (uint32_t)ctx->world;
+        cudaStream_t s = ctx->stream;
+        if (world > PX_MAX_WORLD) return B200BPE_OK;
+        owned_log2 = table_log2;
+        // an inbox region holds what one rank can send one owner after a full count: a local table is
+        // at most half full before it grows, and the owners share its pairs about evenly
+        pb.cap = std::max<uint32_t>(4096u, (1u << table_log2) / world);
+        pb.world = world;
+        pb.rank = (uint32_t)ctx->rank;
+        xbuf_bytes = PX_INBOX_OFF + (size_t)world * pb.cap * 16;
+        B2_CUDA(cudaMalloc(&xbuf, xbuf_bytes));
+        B2_CUDA(cudaMalloc(&owned, sizeof(PairSlot) << owned_log2));
+        B2_CUDA(cudaMalloc(&dlist, sizeof(uint32_t) * DLIST_CAP));
+        B2_CUDA(cudaMalloc(&fill, sizeof(uint32_t) * PX_MAX_WORLD));
+        B2_CUDA(cudaMemsetAsync(xbuf, 0, PX_INBOX_OFF, s));
+        B2_CUDA(cudaMemsetAsync(owned, 0, sizeof(PairSlot) << owned_log2, s));
+        B2_CUDA(cudaMemsetAsync(fill, 0, sizeof(uint32_t) * PX_MAX_WORLD, s));
+        // exchange the IPC handles of the buffers (64 bytes each) with an all-gather
+        cudaIpcMemHandle_t mine{};
+        unsigned long long failed = cudaIpcGetMemHandle(&mine, xbuf) != cudaSuccess ? 1ull : 0ull;
+        cudaGetLastError();
+        static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+        unsigned char* d_h = nullptr;
+        B2_CUDA(cudaMalloc(&d_h, (size_t)world * 64 + 16));
+        B2_CUDA(cudaMemcpyAsync(d_h + (size_t)ctx->rank * 64, &mine, 64, cudaMemcpyHostToDevice, s));
+        int rc = ctx->nccl.AllGather(d_h + (size_t)ctx->rank * 64, d_h, 64, /*ncclUint8*/ 1, ctx->comm, s);
+        if (rc) { cudaFree(d_h); set_last_error("ncclAllGather failed"); return B200BPE_ERR_NCCL; }
+        std::vector<cudaIpcMemHandle_t> all(world);
+        B2_CUDA(cudaMemcpyAsync(all.data(), d_h, (size_t)world * 64, cudaMemcpyDeviceToHost, s));
+        B2_CUDA(cudaStreamSynchronize(s));
+        for (uint32_t p = 0; p < world && !failed; p++) {
+            if ((int)p == ctx->rank) { pb.base[p] = xbuf; continue; }
+            void* ptr = nullptr;
+            if (cudaIpcOpenMemHandle(&ptr, all[p], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); failed = 1ull; break; }
+            mapped[p] = ptr;
+            pb.base[p] = static_cast<unsigned char*>(ptr);
+        }
+        // every rank learns whether every rank succeeded
+        unsigned long long* d_f = reinterpret_cast<unsigned long long*>(d_h + (size_t)world * 64);
+        static_assert(true, "");
+        B2_CUDA(cudaMemcpyAsync(d_f, &failed, 8, cudaMemcpyHostToDevice, s));
+        rc = ctx->nccl.AllReduce(d_f, d_f, 1, /*ncclUint64*/ 5, /*ncclMax*/ 2, ctx->comm, s);
+        if (rc) { cudaFree(d_h); set_last_error("ncclAllReduce failed"); return B200BPE_ERR_NCCL; }
+        B2_CUDA(cudaMemcpyAsync(&failed, d_f, 8, cudaMemcpyDeviceToHost, s));
+        B2_CUDA(cudaStreamSynchronize(s));
+        cudaFree(d_h);
+        if (failed) { release(); return B200BPE_OK; }
+        ok = true;
+        return B200BPE_OK;
+    }
+};
 
 struct Trainer {
     Ctx* ctx = nullptr;
@@ -51,10 +128,15 @@ struct Trainer {
     uint32_t* d_cand = nullptr;   // candidate list of the arg-max (slot indices)
     unsigned long long* d_desc = nullptr;
     DeltaQueues dq{nullptr, nullptr, nullptr, 0, 0};  // incremental mode only
-    Exchange xch;                 // sharded runs only
+    Exchange xch;                 // sharded runs, NCCL exchange
+    PeerExchange px;              // sharded runs, peer-memory exchange (the default)
+    bool peer = false;            // which of the two is in use
+    uint32_t xseq_next = 1;       // peer exchange: sequence number of the next round (continues across resets)
+    uint64_t launches = 0;        // kernel launches of this trainer since creation (graph launches count their nodes)
+    uint32_t graph_kernels = 0;
     cudaGraphExec_t graph = nullptr;
     uint32_t graph_iters = 0;
-    int grid_pc = 1, grid_am = 1, grid_mc = 1;
+    int grid_pc = 1, grid_am = 1, grid_mc = 1, grid_rt = 1, grid_acc = 1;
     // host mirror
     uint32_t merges_done = 0;
     bool early_stop = false;
@@ -88,6 +170,7 @@ Trainer::~Trainer() {
     cudaFree(buf[0]); cudaFree(buf[1]); cudaFree(table); cudaFree(d_state); cudaFree(d_log);
     cudaFree(d_cta_best); cudaFree(d_desc); cudaFree(d_cand); cudaFree(dq.minus); cudaFree(dq.plus); cudaFree(dq.counts);
     xch.release();
+    px.release();
     if (h_state) cudaFreeHost(h_state);
     if (h_log) cudaFreeHost(h_log);
     if (ev_run0) cudaEventDestroy(ev_run0);
@@ -116,7 +199,9 @@ b200bpe_status Trainer::alloc_common() {
     grid_pc = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)sms * PC_CTAS_PER_SM, (nvec + PC_THREADS - 1) / PC_THREADS));
     grid_am = std::max(1, std::min(sms * 4, (int)((1u << table_log2) / (AM_THREADS * 4))));
     const uint64_t ntiles = (n0 + MC_TILE - 1) / MC_TILE;
-    grid_mc = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)sms * 4, ntiles));
+    grid_mc = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)sms * MC_CTAS_PER_SM, ntiles));
+    grid_rt = sms;          // route: a few thousand entries per merge, the whole local table after a full count
+    grid_acc = sms / 2;     // accumulate: as many entries again, from all ranks
     B2_CUDA(cudaMalloc(&d_cta_best, sizeof(CtaBest) * (size_t)(sms * 4 + 1)));
     B2_CUDA(cudaMalloc(&d_cand, sizeof(uint32_t) * CAND_CAP));
     B2_CUDA(cudaMalloc(&d_desc, sizeof(unsigned long long) * (ntiles + 1)));
@@ -144,9 +229,19 @@ b200bpe_status Trainer::alloc_common() {
     B2_CUDA(cudaFuncSetAttribute(k_merge_compact<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_SMEM_BYTES));
     B2_CUDA(cudaFuncSetAttribute(k_merge_compact<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_SMEM_BYTES));
     B2_CUDA(cudaFuncSetAttribute(k_merge_compact<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_SMEM_BYTES));
+    B2_CUDA(cudaFuncSetAttribute(k_merge_compact<false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MC_SMEM_BYTES));
     if (ctx->world > 1) {
-        b200bpe_status s = xch.init(ctx, table_log2);
-        if (s) return s;
+        // The peer-memory exchange needs an incrementally maintained table; FLAG_NCCL_EXCHANGE, a full
+        // recount per merge, or peers that cannot be mapped select the NCCL exchange.
+        if (incremental && !(opts.flags & B200BPE_FLAG_NCCL_EXCHANGE)) {
+            b200bpe_status s = px.init(ctx, table_log2);
+            if (s) return s;
+            peer = px.ok;
+        }
+        if (!peer) {
+            b200bpe_status s = xch.init(ctx, table_log2, opts.exchange_cap);
+            if (s) return s;
+        }
     }
     return B200BPE_OK;
 }
@@ -161,6 +256,7 @@ b200bpe_status Trainer::init_state() {
     } else {
         const int grid = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)ctx->sm_count * 8, (n0 + 255) / 256));
         k_tag_symbols<<<grid, 256, 0, s>>>(d_bytes, has_mask ? d_mask : nullptr, buf[0], n0);
+        launches += 1;
     }
     if (cap_elems > n0) B2_CUDA(cudaMemsetAsync(buf[0] + n0, 0, (cap_elems - n0) * 4, s));
     // The destination buffer starts zeroed, as a fresh WebGPU buffer does; in literal mode its
@@ -171,6 +267,13 @@ b200bpe_status Trainer::init_state() {
     B2_CUDA(cudaMemsetAsync(d_desc, 0, sizeof(unsigned long long) * ((n0 + MC_TILE - 1) / MC_TILE + 1), s));
     if (dq.counts) B2_CUDA(cudaMemsetAsync(dq.counts, 0, (size_t)dq.segments * 8, s));
     std::memset(h_state, 0, sizeof(DevState));
+    if (peer) {
+        B2_CUDA(cudaMemsetAsync(px.owned, 0, sizeof(PairSlot) << px.owned_log2, s));
+        h_state->xseq = xseq_next;
+        h_state->owned = px.owned;
+        h_state->owned_log2 = px.owned_log2;
+        h_state->dlist = px.dlist;
+    }
     h_state->n[0] = (uint32_t)n0;
     h_state->next_id = opts.first_token_id;
     h_state->table_log2 = table_log2;
@@ -179,7 +282,8 @@ b200bpe_status Trainer::init_state() {
     h_state->incremental = incremental ? 1u : 0u;
     h_state->recount = 1u;
     h_state->table = table;
-    h_state->need_scan = 1u;
+    h_state->scan_from = 0u;            // the first arg-max scans the table
+    h_state->presetup_at = 0xFFFFFFFFu;
     h_state->cand_tau = 0xFFFFFFFFu;
     h_state->cand_tau_next = 0xFFFFFFFFu;
     h_state->cand = d_cand;
@@ -204,13 +308,20 @@ __global__ void k_begin_batch(DevState* st, uint32_t target) {
     st->merges_target = target;
     st->target_hit = (st->merges_done >= target) ? 1u : 0u;
 }
-__global__ void k_clear_status(DevState* st, uint32_t table_log2, PairSlot* table) {
+__global__ void k_clear_status(DevState* st, uint32_t table_log2, PairSlot* table, PairSlot* owned, uint32_t owned_log2,
+                               uint32_t* dlist) {
     st->status = DS_OK;
     st->want_grow = 0u;
     st->table_log2 = table_log2;
     st->table = table;
+    st->owned = owned;
+    st->owned_log2 = owned_log2;
+    st->dlist = dlist;
+    st->owned_inserted = 0u;
+    st->dlist_n = 0u;
+    st->occupied = 0u;
     st->recount = 1u;  // the table is new and empty
-    st->need_scan = 1u;
+    st->scan_from = 0u;
     st->cand_tau = 0xFFFFFFFFu;
     st->cand_n = 0u;
 }
@@ -222,27 +333,34 @@ b200bpe_status Trainer::enqueue_merge(int iter, bool timed) {
     auto ev = [&](int k) -> cudaError_t {
         return timed ? cudaEventRecord(kev[(size_t)iter * 8 + k], s) : cudaSuccess;
     };
-    static const bool dbg = getenv("B200BPE_DEBUG_SYNC") != nullptr;
-    auto dsync = [&](const char* what) {
-        if (!dbg) return;
-        cudaError_t e = cudaStreamSynchronize(s);
-        fprintf(stderr, "[b200bpe] iter %d after %s: %s\n", iter, what, cudaGetErrorString(e));
-        fflush(stderr);
-    };
     B2_CUDA(ev(0));
     k_pair_count<PC_SLOTS, PC_THREADS><<<grid_pc, PC_THREADS, PC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], ktable(), d_log);
     B2_CUDA(ev(1));
-    dsync("pair_count");
+    launches += 3;
+    if (peer) {
+        // deltas (or, after a full count, everything) to the owners; owners accumulate and pick; full scan only if the list is stale
+        k_route<<<grid_rt, PX_THREADS, 0, s>>>(d_state, table, px.pb, px.fill);
+        k_accumulate<<<grid_acc, PX_THREADS, 0, s>>>(d_state, px.pb, d_log, 1);
+        B2_CUDA(ev(2));
+        k_argmax_peer<<<grid_am, AM_THREADS, 0, s>>>(d_state, d_cta_best, px.pb, d_log);
+        B2_CUDA(ev(3));
+        k_merge_compact<false, true, true><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, table, dq);
+        B2_CUDA(ev(5));
+        B2_CUDA(ev(4));
+        launches += 2;
+        B2_CUDA(cudaGetLastError());
+        return B200BPE_OK;
+    }
     if (ctx->world > 1) {
         b200bpe_status r = xch.enqueue(ctx, d_state, table, table_log2, d_cta_best, d_log, grid_am);
         if (r) return r;
+        launches += 6;
         B2_CUDA(ev(2));
     } else {
         B2_CUDA(ev(2));
         k_argmax_setup<<<grid_am, AM_THREADS, 0, s>>>(d_state, ktable(), d_cta_best, d_log, 0, 0u);
     }
     B2_CUDA(ev(3));
-    dsync("argmax_setup");
     if (incremental) {
         if (literal) k_merge_compact<true, true><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, ktable(), dq);
         else k_merge_compact<false, true><<<grid_mc, MC_THREADS, MC_SMEM_BYTES, s>>>(d_state, buf[0], buf[1], d_desc, ktable(), dq);
@@ -254,7 +372,6 @@ b200bpe_status Trainer::enqueue_merge(int iter, bool timed) {
     }
     if (!incremental) B2_CUDA(ev(5));
     B2_CUDA(ev(4));
-    dsync("merge_compact");
     B2_CUDA(cudaGetLastError());
     return B200BPE_OK;
 }
@@ -265,10 +382,13 @@ b200bpe_status Trainer::build_graph() {
     if (graph) { cudaGraphExecDestroy(graph); graph = nullptr; }
     cudaStream_t s = ctx->stream;
     cudaGraph_t g = nullptr;
+    const uint64_t launches_before = launches;
     B2_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
     b200bpe_status r = B200BPE_OK;
     for (uint32_t i = 0; i < opts.batch_merges + spare_iters() && r == B200BPE_OK; i++) r = enqueue_merge((int)i, false);
     cudaError_t e = cudaStreamEndCapture(s, &g);
+    graph_kernels = (uint32_t)(launches - launches_before);   // kernels per graph launch
+    launches = launches_before;                                // capturing launched nothing
     if (r != B200BPE_OK) { if (g) cudaGraphDestroy(g); return r; }
     B2_CUDA(e);
     e = cudaGraphInstantiate(&graph, g, 0);
@@ -288,11 +408,18 @@ b200bpe_status Trainer::grow_table() {
     B2_CUDA(cudaMalloc(&table, sizeof(PairSlot) << table_log2));
     B2_CUDA(cudaMemsetAsync(table, 0, sizeof(PairSlot) << table_log2, s));
     grid_am = std::max(1, std::min(ctx->sm_count * 4, (int)((1u << table_log2) / (AM_THREADS * 4))));
-    if (ctx->world > 1) {
-        b200bpe_status r = xch.resize(ctx, table_log2);
+    if (peer) {
+        // the inboxes are sized from the table: new buffers, mapped again by every rank (all ranks grow together)
+        px.release();
+        b200bpe_status r = px.init(ctx, table_log2);
+        if (r) return r;
+        if (!px.ok) { set_last_error("peer buffers could not be mapped again after the table grew"); return B200BPE_ERR_CUDA; }
+    } else if (ctx->world > 1) {
+        b200bpe_status r = xch.resize(ctx, table_log2, opts.exchange_cap);
         if (r) return r;
     }
-    k_clear_status<<<1, 1, 0, s>>>(d_state, table_log2, table);
+    k_clear_status<<<1, 1, 0, s>>>(d_state, table_log2, table, px.owned, px.owned_log2, px.dlist);
+    launches += 1;
     if (graph && ctx->world > 1) { cudaGraphExecDestroy(graph); graph = nullptr; }
     return B200BPE_OK;
 }
@@ -329,22 +456,38 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
         const uint32_t before = merges_done;
         const uint32_t batch = batch_target - before;
         k_begin_batch<<<1, 1, 0, s>>>(d_state, batch_target);
+        launches += 1;
         if (use_graph) {
             if (!graph) { b200bpe_status r = build_graph(); if (r) return r; }
             B2_CUDA(cudaGraphLaunch(graph, s));
+            launches += graph_kernels;
         } else {
             for (uint32_t i = 0; i < batch + spare_iters(); i++) { b200bpe_status r = enqueue_merge((int)i, timed); if (r) return r; }
         }
         // literal mode, incremental table: inside a batch the next merge's count kernel finishes the
         // table update of a merge; the batch's last merge gets it here
-        if (incremental && opts.compat_mode == B200BPE_COMPAT_LITERAL)
+        if (incremental && opts.compat_mode == B200BPE_COMPAT_LITERAL) {
             k_literal_tail<<<std::max(1, ctx->sm_count), 256, 0, s>>>(d_state, buf[0], buf[1], ktable());
+            launches += 1;
+        }
+        // Sharded: a status that the batch's last merge kernel raised on one rank (table full, a wait
+        // that ran out) reaches every rank before the host looks at it, so that all ranks grow, resize
+        // or give up together.
+        if (peer) {
+            k_batch_sync<<<1, 32, 0, s>>>(d_state, px.pb);
+            launches += 1;
+        } else if (ctx->world > 1) {
+            b200bpe_status r = xch.enqueue_status_sync(ctx, d_state);
+            if (r) return r;
+            launches += 2;
+        }
         // One read-back per batch: the control block and this batch's slice of the merge log
         // (trainer.js:248-267 reads the same two things).
         B2_CUDA(cudaMemcpyAsync(h_state, d_state, sizeof(DevState), cudaMemcpyDeviceToHost, s));
         B2_CUDA(cudaMemcpyAsync(h_log + (size_t)before * 4, d_log + (size_t)before * 4, (size_t)batch * 16,
                                 cudaMemcpyDeviceToHost, s));
         B2_CUDA(cudaStreamSynchronize(s));
+        if (peer) xseq_next = h_state->xseq;
         const uint32_t done_now = h_state->merges_done;
         const uint32_t got = done_now - before;
         if (timed) {
@@ -387,7 +530,7 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
         if (got == 0 && !h_state->early_stop && h_state->status == DS_OK && !h_state->want_grow) {
             // a batch of one or two iterations can be used up by an arg-max that only found its
             // candidate list stale (the merge then follows in the next iteration)
-            if (!(h_state->need_scan && ++idle_batches <= 4)) {
+            if (!(h_state->iter_no >= h_state->scan_from && ++idle_batches <= 4)) {
                 set_last_error("a batch made no progress");
                 return B200BPE_ERR_INTERNAL;
             }
@@ -404,7 +547,8 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
         cur_n = h_state->n[h_state->epoch & 1];
         early_stop = h_state->early_stop != 0;
         table_replaced = false;
-        if (ctx->world > 1 && (h_state->status == DS_BUCKET_FULL || h_state->status == DS_OK)) {
+        if (peer && h_state->status == DS_BUCKET_FULL) h_state->status = DS_TABLE_FULL;   // an inbox too small for the table's pairs: grow both
+        if (ctx->world > 1 && !peer && (h_state->status == DS_BUCKET_FULL || h_state->status == DS_OK)) {
             // sharded runs: resize the exchange buckets to the traffic seen (same decision on every rank)
             const bool over = h_state->status == DS_BUCKET_FULL;
             if (over && xch.cap >= xch.cap_alloc) { h_state->status = DS_TABLE_FULL; }
@@ -413,7 +557,7 @@ b200bpe_status Trainer::run(uint32_t max_merges, uint32_t* merges_out, uint32_t*
                 if (over) {
                     // some pairs never reached their owners: count again, from an empty local table
                     B2_CUDA(cudaMemsetAsync(table, 0, sizeof(PairSlot) << table_log2, s));
-                    k_clear_status<<<1, 1, 0, s>>>(d_state, table_log2, table);
+                    k_clear_status<<<1, 1, 0, s>>>(d_state, table_log2, table, nullptr, 0u, nullptr);
                     h_state->status = DS_OK;
                 }
             }
@@ -472,10 +616,12 @@ static b200bpe_status check_opts(const Ctx* ctx, const b200bpe_train_opts* in, b
 
 static b200bpe_status make_trainer(b200bpe_ctx* c, const uint8_t* bytes, const uint8_t* mask, const uint32_t* symbols,
                                    uint64_t n, bool device_inputs, const b200bpe_train_opts* opts, Trainer** out) {
-    if (!c || !out || (!bytes && !symbols)) return B200BPE_ERR_BAD_ARG;
-    // A shard of a sharded job may be empty; a single-GPU corpus may not (trainer.js:161-163).
-    if (n == 0 && c->c.world == 1) return B200BPE_ERR_EMPTY_CORPUS;
-    if (n >= 0xFFFFFFF0ull) return B200BPE_ERR_BAD_ARG;  // per-GPU symbol indices are 32-bit
+    if (!c || !out) return B200BPE_ERR_BAD_ARG;
+    // A shard of a sharded job may be empty (then without any buffer); a single-GPU corpus may not (trainer.js:161-163).
+    if (n == 0 && c->c.world == 1) return (!bytes && !symbols) ? B200BPE_ERR_BAD_ARG : B200BPE_ERR_EMPTY_CORPUS;
+    if (n != 0 && !bytes && !symbols) return B200BPE_ERR_BAD_ARG;
+    // per-GPU symbol indices are 32-bit, and the merge kernel adds up to two tiles to an index before it tests it
+    if (n >= 0xFFFFFFF0ull - 2ull * MC_TILE) return B200BPE_ERR_BAD_ARG;
     B2_CUDA(cudaSetDevice(c->c.device));
     Trainer* t = new Trainer();
     t->ctx = &c->c;
@@ -489,7 +635,7 @@ static b200bpe_status make_trainer(b200bpe_ctx* c, const uint8_t* bytes, const u
     const size_t nb = std::max<uint64_t>(n, 1);
     if (symbols) {
         if (cudaMalloc(&t->d_sym_init, nb * 4) != cudaSuccess) return fail(B200BPE_ERR_OOM);
-        if (cudaMemcpyAsync(t->d_sym_init, symbols, n * 4, device_inputs ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, s) != cudaSuccess)
+        if (n && cudaMemcpyAsync(t->d_sym_init, symbols, n * 4, device_inputs ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, s) != cudaSuccess)
             return fail(B200BPE_ERR_CUDA);
     } else if (device_inputs) {
         t->own_inputs = false;
@@ -498,10 +644,10 @@ static b200bpe_status make_trainer(b200bpe_ctx* c, const uint8_t* bytes, const u
         t->has_mask = mask != nullptr;
     } else {
         if (cudaMalloc(&t->d_bytes, nb) != cudaSuccess) return fail(B200BPE_ERR_OOM);
-        if (cudaMemcpyAsync(t->d_bytes, bytes, n, cudaMemcpyHostToDevice, s) != cudaSuccess) return fail(B200BPE_ERR_CUDA);
+        if (n && cudaMemcpyAsync(t->d_bytes, bytes, n, cudaMemcpyHostToDevice, s) != cudaSuccess) return fail(B200BPE_ERR_CUDA);
         if (mask) {
             if (cudaMalloc(&t->d_mask, nb) != cudaSuccess) return fail(B200BPE_ERR_OOM);
-            if (cudaMemcpyAsync(t->d_mask, mask, n, cudaMemcpyHostToDevice, s) != cudaSuccess) return fail(B200BPE_ERR_CUDA);
+            if (n && cudaMemcpyAsync(t->d_mask, mask, n, cudaMemcpyHostToDevice, s) != cudaSuccess) return fail(B200BPE_ERR_CUDA);
             t->has_mask = true;
         }
     }
@@ -592,7 +738,16 @@ b200bpe_status b200bpe_trainer_pair_counts(b200bpe_trainer* h, uint64_t* keys_ou
                 t->d_state, t->buf[0], t->buf[1], t->table, t->d_log);
         PairSlot* tab = t->table;
         uint32_t tl2 = t->table_log2;
-        if (t->ctx->world > 1) {
+        if (t->peer) {
+            // The owned table holds the global counts of this rank's pairs, short of what still sits in
+            // the ranks' local tables: the deltas of the last merge, or (a rebuild pending) the fresh full
+            // counts.  One exchange round without a pick brings it up to date (collective: every rank calls).
+            k_route<<<t->grid_rt, PX_THREADS, 0, s>>>(t->d_state, t->table, t->px.pb, t->px.fill);
+            k_accumulate<<<t->grid_acc, PX_THREADS, 0, s>>>(t->d_state, t->px.pb, t->d_log, 0);
+            k_batch_sync<<<1, 32, 0, s>>>(t->d_state, t->px.pb);
+            tab = t->px.owned;
+            tl2 = t->px.owned_log2;
+        } else if (t->ctx->world > 1) {
             b200bpe_status r = t->xch.enqueue_counts_only(t->ctx, t->d_state, t->table, t->table_log2);
             if (r) return r;
             tab = t->xch.owned;
@@ -609,8 +764,9 @@ b200bpe_status b200bpe_trainer_pair_counts(b200bpe_trainer* h, uint64_t* keys_ou
         // that is up to date stays; one that was only counted for this call is emptied, because the
         // rebuild that is still pending starts from an empty table.
         const bool owned_table = tab != t->table;
-        k_dump_table<<<t->ctx->sm_count * 4, 256, 0, s>>>(tab, 1u << tl2, dk, dc, dcap, dn, (owned_table || !as_is) ? 1 : 0);
-        if (owned_table && !as_is) B2_CUDA(cudaMemsetAsync(t->table, 0, sizeof(PairSlot) << t->table_log2, s));
+        const bool clear = t->peer ? !as_is : (owned_table || !as_is);
+        k_dump_table<<<t->ctx->sm_count * 4, 256, 0, s>>>(tab, 1u << tl2, dk, dc, dcap, dn, clear ? 1 : 0);
+        if (owned_table && !as_is && !t->peer) B2_CUDA(cudaMemsetAsync(t->table, 0, sizeof(PairSlot) << t->table_log2, s));
         uint32_t nd = 0;
         B2_CUDA(cudaMemcpyAsync(&nd, dn, 4, cudaMemcpyDeviceToHost, s));
         B2_CUDA(cudaMemcpyAsync(t->h_state, t->d_state, sizeof(DevState), cudaMemcpyDeviceToHost, s));
@@ -620,9 +776,10 @@ b200bpe_status b200bpe_trainer_pair_counts(b200bpe_trainer* h, uint64_t* keys_ou
             cudaFree(dk); cudaFree(dc); cudaFree(dn);
             // the rebuild that k_clear_status asks for starts from an empty local table
             B2_CUDA(cudaMemsetAsync(t->table, 0, sizeof(PairSlot) << t->table_log2, s));
-            k_clear_status<<<1, 1, 0, s>>>(t->d_state, t->table_log2, t->table);
+            k_clear_status<<<1, 1, 0, s>>>(t->d_state, t->table_log2, t->table, t->px.owned, t->px.owned_log2, t->px.dlist);
             return B200BPE_ERR_CAPACITY;
         }
+        if (t->peer) t->xseq_next = t->h_state->xseq;
         const bool full = t->h_state->status == DS_TABLE_FULL;
         if (!full) {
             const uint32_t m = std::min(nd, dcap);
@@ -630,10 +787,15 @@ b200bpe_status b200bpe_trainer_pair_counts(b200bpe_trainer* h, uint64_t* keys_ou
             if (counts_out) B2_CUDA(cudaMemcpy(counts_out, dc, (size_t)m * 4, cudaMemcpyDeviceToHost));
         }
         cudaFree(dk); cudaFree(dc); cudaFree(dn);
+        if (t->peer && !as_is)   // the owned table was emptied by the dump: its insert count starts over, the rebuild stays pending
+            k_clear_status<<<1, 1, 0, s>>>(t->d_state, t->table_log2, t->table, t->px.owned, t->px.owned_log2, t->px.dlist);
         if (!full) {
             *n_distinct_out = nd;
             return nd > cap ? B200BPE_ERR_CAPACITY : B200BPE_OK;
         }
+        // Sharded: growing is a collective step (buffers are mapped between ranks, bucket sizes must
+        // agree), and this call has no way to make every rank take it: report the full table instead.
+        if (t->ctx->world > 1) return B200BPE_ERR_TABLE_FULL;
         b200bpe_status r = t->grow_table();
         if (r) return r;
     }
@@ -643,6 +805,18 @@ b200bpe_status b200bpe_trainer_pair_counts(b200bpe_trainer* h, uint64_t* keys_ou
 b200bpe_status b200bpe_trainer_kernel_stats(b200bpe_trainer* h, b200bpe_kernel_stats* out) {
     if (!h || !out) return B200BPE_ERR_BAD_ARG;
     *out = h->t->stats;
+    return B200BPE_OK;
+}
+
+b200bpe_status b200bpe_trainer_launches(b200bpe_trainer* h, uint64_t* n) {
+    if (!h || !n) return B200BPE_ERR_BAD_ARG;
+    *n = h->t->launches;
+    return B200BPE_OK;
+}
+
+b200bpe_status b200bpe_trainer_exchange_kind(b200bpe_trainer* h, uint32_t* kind) {
+    if (!h || !kind) return B200BPE_ERR_BAD_ARG;
+    *kind = h->t->ctx->world == 1 ? 0u : (h->t->peer ? 1u : 2u);
     return B200BPE_OK;
 }
 

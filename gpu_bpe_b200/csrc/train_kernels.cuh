@@ -26,11 +26,39 @@ constexpr int PC_LOCAL_PROBES = 2;   // linear probes in shared memory before go
 constexpr int TABLE_MAX_PROBE = 1024;
 constexpr int AM_THREADS = 256;
 constexpr int MC_THREADS = 256;
-constexpr int MC_ROWS = 4;                               // uint4 rows per thread per sub-tile
-constexpr int MC_SUB = MC_THREADS * 4 * MC_ROWS;         // 4,096 symbols per sub-tile
-constexpr int MC_SUBS = 3;                               // sub-tiles per tile (48 KB of shared memory: four CTAs per SM)
-constexpr int MC_TILE = MC_SUB * MC_SUBS;                // 12,288 symbols per tile: one look-back each
-constexpr int MC_SMEM_BYTES = (MC_TILE + 8) * 4;         // the tile and its edges (dynamic shared memory)
+#ifndef B200BPE_MC_ROWS
+#define B200BPE_MC_ROWS 4
+#endif
+#ifndef B200BPE_MC_SUBS
+#define B200BPE_MC_SUBS 3
+#endif
+#ifndef B200BPE_MC_NBUF
+#define B200BPE_MC_NBUF 2
+#endif
+#ifndef B200BPE_MC_UNROLL
+#define B200BPE_MC_UNROLL 0
+#endif
+#if B200BPE_MC_UNROLL
+#define MC_UNROLL_SUBS _Pragma("unroll")
+#else
+#define MC_UNROLL_SUBS _Pragma("unroll 1")
+#endif
+#ifndef B200BPE_MC_CTAS
+#define B200BPE_MC_CTAS 2
+#endif
+constexpr int MC_ROWS = B200BPE_MC_ROWS;                 // uint4 rows per thread per sub-tile (1..4)
+constexpr int MC_SUB = MC_THREADS * 4 * MC_ROWS;         // symbols per sub-tile
+constexpr int MC_SUBS = B200BPE_MC_SUBS;                 // sub-tiles per tile (1..4)
+constexpr int MC_TILE = MC_SUB * MC_SUBS;                // symbols per tile: one look-back each
+constexpr int MC_NBUF = B200BPE_MC_NBUF;                 // tile buffers per CTA (the pipeline needs at least two)
+constexpr int MC_CTAS_PER_SM = B200BPE_MC_CTAS;
+constexpr int MC_SMEM_BYTES = MC_NBUF * (MC_TILE + 8) * 4;  // the tiles and their edges (dynamic shared memory)
+// Per row of a span the decisions of pass 1 take one byte of a word; these masks select the bytes of the rows in use.
+constexpr uint32_t MC_ROWBYTES = MC_ROWS == 4 ? 0xFFFFFFFFu : ((1u << (8 * (MC_ROWS & 3))) - 1u);  // bytes 0..ROWS-1
+constexpr uint32_t MC_KEEP_ALL = 0x0F0F0F0Fu & MC_ROWBYTES;                        // every own symbol kept
+constexpr uint32_t MC_NOTLAST = MC_ROWBYTES >> 8;                                  // bytes 0..ROWS-2
+constexpr int MC_LASTROW_SHIFT = 8 * (MC_ROWS - 1);                                // bit 0 of the last row's byte
+static_assert(MC_NBUF >= 2 && MC_ROWS >= 1 && MC_ROWS <= 4 && MC_SUBS >= 1 && MC_SUBS <= 4, "merge kernel shape");
 constexpr int MC_WARPS = MC_THREADS / 32;
 constexpr uint32_t LOOKBACK_MAX_SPINS = 1u << 22;        // bounded wait; then DS_LOOKBACK_TIMEOUT
 constexpr uint32_t BULK_MAX_SPINS = 1u << 20;            // bounded wait for a bulk copy; then DS_LOOKBACK_TIMEOUT
@@ -81,8 +109,35 @@ __device__ __forceinline__ void table_add(PairSlot* __restrict__ table, uint32_t
                                           uint32_t h, uint32_t c, DevState* st) {
     table_add(table, logC, key, h, c, st, c >= 0x80000000u ? 0xFFFFFFFFu : st->cand_tau);
 }
-__device__ __forceinline__ void void_candidates(DevState* st) {
-    st->need_scan = 1u;
+// Sharded runs with the peer-memory exchange: the local table only collects the signed pair deltas
+// of one merge (it is emptied when they are sent to the pairs' owners); the first entry of a slot
+// appends the slot to the list of slots to send.
+constexpr uint32_t DLIST_CAP = 1u << 20;
+__device__ __forceinline__ void delta_add(PairSlot* __restrict__ table, uint32_t logC, unsigned long long key, uint32_t h,
+                                          uint32_t c, DevState* st) {
+    const uint32_t mask = (1u << logC) - 1u;
+    uint32_t slot = h >> (32 - logC);
+    for (int p = 0; p < TABLE_MAX_PROBE; p++) {
+        unsigned long long k = __ldcg(&table[slot].key);
+        if (k == 0ull) {
+            k = atomicCAS(&table[slot].key, 0ull, key);
+            if (k == 0ull) {
+                k = key;
+                const uint32_t i = atomicAdd(&st->dlist_n, 1u);
+                if (i < DLIST_CAP) st->dlist[i] = slot;
+                else atomicExch(&st->status, (uint32_t)DS_TABLE_FULL);
+            }
+        }
+        if (k == key) { atomicAdd(&table[slot].count, c); return; }
+        slot = (slot + 1) & mask;
+    }
+    atomicExch(&st->status, (uint32_t)DS_TABLE_FULL);
+}
+
+// No usable candidate list: every arg-max from iteration `from` on scans the whole table, until one
+// of those scans has built a new list.
+__device__ __forceinline__ void void_candidates(DevState* st, uint32_t from) {
+    st->scan_from = from;
     st->cand_tau = 0xFFFFFFFFu;
     st->cand_n = 0u;
 }
@@ -177,7 +232,7 @@ __device__ __forceinline__ bool smem_count(uint32_t* __restrict__ skey, uint32_t
 }
 
 __device__ __forceinline__ void warp_best(uint32_t& c, unsigned long long& k);
-__device__ __forceinline__ void void_candidates(DevState* st);
+__device__ __forceinline__ void void_candidates(DevState* st, uint32_t from);
 __device__ __forceinline__ void setup_merge(DevState* st, const DevState* rd, uint32_t best_count,
                                             unsigned long long best_key, uint32_t* __restrict__ log);
 
@@ -205,21 +260,24 @@ k_pair_count(DevState* __restrict__ st, const uint32_t* __restrict__ buf0, const
         s_tail = snap.tail_fix;
         // Nothing to count and a usable candidate list: the last CTA of this launch to finish can
         // pick the next merge right here, and the arg-max kernel of this iteration has nothing to do.
-        s_fuse = (snap.incremental != 0u && snap.world == 1u && snap.recount == 0u && snap.need_scan == 0u &&
+        s_fuse = (snap.incremental != 0u && snap.world == 1u && snap.recount == 0u && snap.iter_no < snap.scan_from &&
                   snap.early_stop == 0u && snap.target_hit == 0u && snap.status == DS_OK) ? 1u : 0u;
     }
     __syncthreads();
     // literal mode, incremental table: finish the table update of the merge before this one.  When
     // there is nothing to count, a part of the grid is plenty for that (the tail is as long as the
-    // merged pair's count) and the other CTAs leave at once.
+    // merged pair's count) and the other CTAs have nothing to do.
     const uint32_t workers = s_idle ? min(gridDim.x, (uint32_t)PC_IDLE_CTAS) : gridDim.x;
-    if (blockIdx.x >= workers) return;
-    if (s_tail) literal_tail_fix(st, &snap, buf0, buf1, table, workers);
+    if (s_tail && blockIdx.x < workers) literal_tail_fix(st, &snap, buf0, buf1, table, workers);
     if (s_idle) {
         if (!s_fuse) return;
+        // Every CTA of the launch arrives here, workers or not, and the one that arrives last picks
+        // the merge: by then every CTA has taken its copy of the control block, so what the pick
+        // writes cannot send a late CTA down another branch.  (k1_done is put back to zero by the
+        // merge kernel of the iteration.)
         __threadfence();   // this CTA's table updates and list entries are out before it is counted as done
         __syncthreads();
-        if (threadIdx.x == 0) s_last = (atomicAdd(&st->k1_done, 1u) == workers - 1u) ? 1u : 0u;
+        if (threadIdx.x == 0) s_last = (atomicAdd(&st->k1_done, 1u) == gridDim.x - 1u) ? 1u : 0u;
         __syncthreads();
         if (!s_last) return;
         __threadfence();
@@ -240,17 +298,16 @@ k_pair_count(DevState* __restrict__ st, const uint32_t* __restrict__ buf0, const
         if (threadIdx.x == 0) {
             for (int w = 1; w < THREADS / 32; w++)
                 if (is_better(r_c[w], r_k[w], bc, bk)) { bc = r_c[w]; bk = r_k[w]; }
-            st->k1_done = 0u;
             snap.status = __ldcg(&st->status);   // the tail fix may have found the table full
             // The list decides as long as its best count is at least its threshold: everything
             // else was below the threshold at the last full scan and has not crossed it since.
             if (bc >= snap.cand_tau && cand_n < CAND_CAP && snap.since_scan < CAND_MAX_AGE) {
                 st->since_scan = snap.since_scan + 1u;
                 setup_merge(st, &snap, bc, bk, log);
-                st->presetup = 1u;
+                st->presetup_at = snap.iter_no;
             } else {
                 // the arg-max kernel of this iteration scans the table
-                void_candidates(st);
+                void_candidates(st, snap.iter_no);
                 st->cand_tau_next = max(2u, min(snap.cand_tau, snap.cand_tau_next) / 2u);
             }
         }
@@ -350,7 +407,7 @@ __device__ __forceinline__ void warp_best(uint32_t& c, unsigned long long& k) {
 __device__ __forceinline__ void setup_merge(DevState* st, const DevState* rd, uint32_t best_count,
                                             unsigned long long best_key, uint32_t* __restrict__ log) {
     st->tail_fix = 0u;
-    if (rd->status != DS_OK) { st->active = 0u; st->recount = 1u; void_candidates(st); return; }
+    if (rd->status != DS_OK) { st->active = 0u; st->recount = 1u; void_candidates(st, rd->iter_no + 1u); return; }
     const uint32_t next_id = rd->next_id;
     if (best_count < 2u || next_id > TOKEN_MASK) {
         st->early_stop = 1u;
@@ -371,7 +428,7 @@ __device__ __forceinline__ void setup_merge(DevState* st, const DevState* rd, ui
     // update rule does not cover; the table is emptied and rebuilt by a full count instead.
     const uint32_t recount = rd->incremental ? (a == b ? 1u : 0u) : 1u;
     st->recount = recount;
-    if (recount) void_candidates(st);   // the table is about to be rebuilt
+    if (recount) void_candidates(st, rd->iter_no + 1u);   // the table is about to be rebuilt
     st->tail_fix = (rd->incremental && rd->literal && a != b) ? 1u : 0u;
 }
 __device__ __forceinline__ void setup_merge(DevState* st, uint32_t best_count, unsigned long long best_key,
@@ -391,18 +448,16 @@ k_argmax_setup(DevState* __restrict__ st, PairSlot* table, CtaBest* __restrict__
     __shared__ bool is_last;
     // One 16-byte load per thread copies the control block into shared memory: everything the
     // kernel needs to know arrives in one round trip instead of a chain of dependent loads.
-    // Nothing in it changes before every CTA has taken its copy: only the last CTA to finish
-    // (or the one CTA of a candidate-list pass) writes the block.
+    // Whatever decides a CTA's branch is the same in every copy: the block is written by the CTA
+    // that arrives last only (every CTA arrives, on every path that writes), and flags meant for
+    // later kernels are stored as iteration numbers.
     __shared__ __align__(16) DevState snap;
     static_assert(sizeof(DevState) % 16 == 0 && sizeof(DevState) / 16 <= AM_THREADS, "control block copy");
     if (threadIdx.x < sizeof(DevState) / 16)
         reinterpret_cast<uint4*>(&snap)[threadIdx.x] = __ldcg(reinterpret_cast<const uint4*>(st) + threadIdx.x);
     __syncthreads();
     // The count kernel of this iteration has already chosen the merge from the candidate list.
-    if (snap.presetup) {
-        if (blockIdx.x == 0 && threadIdx.x == 0) st->presetup = 0u;
-        return;
-    }
+    if (snap.presetup_at == snap.iter_no) return;
     // Once the run has stopped, nothing is left for the merge kernel to apply.
     if (snap.early_stop | snap.target_hit) {
         if (blockIdx.x == 0 && threadIdx.x == 0) { st->active = 0u; st->tail_fix = 0u; }
@@ -415,28 +470,44 @@ k_argmax_setup(DevState* __restrict__ st, PairSlot* table, CtaBest* __restrict__
     uint32_t bc = 0, occ = 0;
     unsigned long long bk = 0ull;
     const uint32_t stride = gridDim.x * AM_THREADS;
-    // Incremental table, single GPU: most merges only look at the candidate list.  `need_scan`,
-    // like the stop flags, is written by the last CTA to finish (or between kernels) only.
+    // Incremental table, single GPU: most merges only look at the candidate list; a full scan is due
+    // from iteration `scan_from` on.
     const bool listed = mode == 0 && snap.incremental != 0u;
-    const bool use_list = listed && snap.need_scan == 0u;
+    const bool use_list = listed && snap.iter_no < snap.scan_from;
     const uint32_t tau_scan = listed ? snap.cand_tau_next : 0xFFFFFFFFu;   // threshold of the list a full scan builds
     uint32_t* __restrict__ cand = snap.cand;
     if (use_list) {
-        // one CTA is enough for a list of at most a few thousand slots, and it needs no second phase
-        if (blockIdx.x != 0) return;
-        const uint32_t n = min(snap.cand_n, CAND_CAP);
-        for (uint32_t i = threadIdx.x; i < n; i += AM_THREADS) {
-            const uint4 q = __ldcg(t4 + cand[i]);
-            const unsigned long long key = ((unsigned long long)q.y << 32) | q.x;
-            if (key != 0ull && is_better(q.z, key, bc, bk)) { bc = q.z; bk = key; }
+        // One CTA is enough for a list of at most a few thousand slots.  The others only arrive; the
+        // CTA that arrives last (nearly always CTA 0) takes CTA 0's result and sets the merge up.
+        if (blockIdx.x == 0) {
+            const uint32_t n = min(snap.cand_n, CAND_CAP);
+            for (uint32_t i = threadIdx.x; i < n; i += AM_THREADS) {
+                const uint4 q = __ldcg(t4 + cand[i]);
+                const unsigned long long key = ((unsigned long long)q.y << 32) | q.x;
+                if (key != 0ull && is_better(q.z, key, bc, bk)) { bc = q.z; bk = key; }
+            }
+            warp_best(bc, bk);
+            const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+            if (lane == 0) { sc[warp] = bc; sk[warp] = bk; }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                for (int w = 1; w < AM_THREADS / 32; w++)
+                    if (is_better(sc[w], sk[w], bc, bk)) { bc = sc[w]; bk = sk[w]; }
+                cta_best[0].key = bk;
+                cta_best[0].count = bc;
+            }
         }
-        warp_best(bc, bk);
-        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-        if (lane == 0) { sc[warp] = bc; sk[warp] = bk; }
-        __syncthreads();
         if (threadIdx.x == 0) {
-            for (int w = 1; w < AM_THREADS / 32; w++)
-                if (is_better(sc[w], sk[w], bc, bk)) { bc = sc[w]; bk = sk[w]; }
+            __threadfence();
+            is_last = atomicAdd(&st->argmax_done, 1u) == gridDim.x - 1;
+        }
+        __syncthreads();
+        if (!is_last) return;
+        if (threadIdx.x == 0) {
+            __threadfence();
+            st->argmax_done = 0u;
+            bc = __ldcg(&cta_best[0].count);
+            bk = __ldcg(&cta_best[0].key);
             // The list decides as long as its best count is at least its threshold: everything
             // else was below the threshold at the last full scan and has not crossed it since.
             if (bc >= snap.cand_tau && snap.cand_n < CAND_CAP && snap.since_scan < CAND_MAX_AGE) {
@@ -444,7 +515,7 @@ k_argmax_setup(DevState* __restrict__ st, PairSlot* table, CtaBest* __restrict__
                 setup_merge(st, &snap, bc, bk, log);
             } else {
                 // no merge in this iteration; the next arg-max scans the table
-                void_candidates(st);
+                void_candidates(st, snap.iter_no + 1u);
                 st->cand_tau_next = max(2u, min(snap.cand_tau, snap.cand_tau_next) / 2u);
                 st->active = 0u;
                 st->tail_fix = 0u;
@@ -527,15 +598,15 @@ k_argmax_setup(DevState* __restrict__ st, PairSlot* table, CtaBest* __restrict__
                 if (tau_scan == 0xFFFFFFFFu || st->cand_n >= CAND_CAP) {
                     // no usable list yet (first scan, or too many slots above the threshold): scan again next time
                     const uint32_t over = st->cand_n >= CAND_CAP ? 1u : 0u;
-                    void_candidates(st);
+                    void_candidates(st, snap.iter_no + 1u);
                     st->cand_tau_next = over ? min(0x7FFFFFFFu, tau_scan) * 2u : max(2u, bc / 2u);
                 } else {
-                    st->need_scan = 0u;
+                    st->scan_from = SCAN_NEVER;
                     st->cand_tau = tau_scan;
                     st->cand_tau_next = max(2u, bc / 2u);
                 }
             }
-            setup_merge(st, bc, bk, log);
+            setup_merge(st, &snap, bc, bk, log);
         } else {
             const uint32_t pair32 = ((uint32_t)(bk >> 32) << 16) | ((uint32_t)bk & 0xFFFFu);
             st->best_packed = ((unsigned long long)bc << 32) | (unsigned long long)(~pair32);
@@ -608,7 +679,7 @@ struct DeltaQueues {
 
 __device__ __noinline__ void queue_deltas(DevState* st, PairSlot* __restrict__ table, DeltaQueues dq, uint32_t* qcnt, uint32_t s0, uint4 own,
                                           uint32_t s5, uint32_t y31, uint32_t z31, uint32_t i0, uint32_t N, bool interior,
-                                          uint32_t A, uint32_t B, uint32_t NW, int lane, uint32_t logC) {
+                                          uint32_t A, uint32_t B, uint32_t NW, int lane, uint32_t logC, bool shard) {
     uint32_t s[8] = {s0, own.x, own.y, own.z, own.w, s5, 0u, 0u};
     s[6] = __shfl_down_sync(0xFFFFFFFFu, own.y, 1);
     s[7] = __shfl_down_sync(0xFFFFFFFFu, own.z, 1);
@@ -676,7 +747,8 @@ __device__ __noinline__ void queue_deltas(DevState* st, PairSlot* __restrict__ t
             if (base_m < dq.seg_cap) seg_m[base_m] = km[t];
             else {
                 const unsigned long long key = ((unsigned long long)(km[t] >> 16) << 32) | (km[t] & 0xFFFFu);
-                table_add(table, logC, key, hash_pair(key), 0xFFFFFFFFu, st);
+                if (shard) delta_add(table, logC, key, hash_pair(key), 0xFFFFFFFFu, st);
+                else table_add(table, logC, key, hash_pair(key), 0xFFFFFFFFu, st);
             }
             base_m++;
         }
@@ -684,7 +756,8 @@ __device__ __noinline__ void queue_deltas(DevState* st, PairSlot* __restrict__ t
             if (base_p < dq.seg_cap) seg_p[base_p] = kp[t];
             else {
                 const unsigned long long key = ((unsigned long long)(kp[t] >> 16) << 32) | (kp[t] & 0xFFFFu);
-                table_add(table, logC, key, hash_pair(key), 1u, st);
+                if (shard) delta_add(table, logC, key, hash_pair(key), 1u, st);
+                else table_add(table, logC, key, hash_pair(key), 1u, st);
             }
             base_p++;
         }
@@ -695,7 +768,7 @@ __device__ __noinline__ void queue_deltas(DevState* st, PairSlot* __restrict__ t
 // of a warp are combined first (match-any), so a popular neighbour pair costs one atomic per warp.
 // The segment's counters are cleared at the end.
 __device__ __forceinline__ void apply_segment(DevState* st, DeltaQueues dq, const uint32_t* qcnt, uint32_t g, PairSlot* __restrict__ table,
-                                              uint32_t logC) {
+                                              uint32_t logC, bool shard) {
     const int lane = threadIdx.x & 31;
     const uint32_t nm = min(qcnt[0], dq.seg_cap), np = min(qcnt[1], dq.seg_cap);
     const uint32_t total = nm + np;
@@ -716,7 +789,8 @@ __device__ __forceinline__ void apply_segment(DevState* st, DeltaQueues dq, cons
             if (lane == __ffs(peers) - 1) {
                 const unsigned long long key = ((unsigned long long)(k32 >> 16) << 32) | (k32 & 0xFFFFu);
                 const uint32_t c = __popc(peers);
-                table_add(table, logC, key, hash_pair(key), neg ? (0u - c) : c, st, tau);
+                if (shard) delta_add(table, logC, key, hash_pair(key), neg ? (0u - c) : c, st);
+                else table_add(table, logC, key, hash_pair(key), neg ? (0u - c) : c, st, tau);
             }
         }
     }
@@ -787,16 +861,26 @@ __device__ unsigned long long g_phase_cycles[8];
 #define PHASE_MARK(k) do {} while (0)
 #endif
 
-template <bool LITERAL, bool INCR>
-__global__ void __launch_bounds__(MC_THREADS, 4)
+// SHARD (sharded runs with the peer-memory exchange): the deltas go into the local delta table for
+// the route kernel, and a merge of two equal symbols empties this rank's table of owned pairs.
+template <bool LITERAL, bool INCR, bool SHARD = false>
+__global__ void __launch_bounds__(MC_THREADS, MC_CTAS_PER_SM)
 k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsigned long long* __restrict__ desc,
                 PairSlot* table, DeltaQueues dq) {
-    extern __shared__ __align__(16) uint32_t mc_smem[];  // 4 words (the last: left edge), the tile, 4 words (right edge)
-    uint32_t* const in = mc_smem + 4;
-    __shared__ __align__(8) unsigned long long bar;
-    __shared__ uint32_t span_cnt[MC_SUBS * MC_WARPS], lb_sum[MC_WARPS], lb_found[MC_WARPS];
-    __shared__ uint32_t s_tile, s_next, s_fail;
+    // MC_NBUF tile buffers, each: 4 words (the last: left edge), the tile, 4 words (right edge)
+    extern __shared__ __align__(16) uint32_t mc_smem[];
+    constexpr uint32_t BUF_WORDS = MC_TILE + 8;
+    __shared__ __align__(8) unsigned long long bar[MC_NBUF];
+    __shared__ uint32_t span_cnt[MC_NBUF][MC_SUBS * MC_WARPS], lb_sum[MC_WARPS], lb_found[MC_WARPS];
+    __shared__ uint32_t s_tid[MC_NBUF], s_fail;   // s_tid[j % MC_NBUF]: the tile of this CTA's j-th turn (>= ntiles: none)
     __shared__ uint32_t s_qcnt[2];  // entries reserved in this CTA's segments of the minus and plus queues
+    // The iteration ends here: one thread advances its number and clears the arrival counters of the
+    // count and arg-max kernels (nobody in this kernel reads any of the three).
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        st->iter_no = st->iter_no + 1u;
+        st->k1_done = 0u;
+        st->argmax_done = 0u;
+    }
     // `active`, `k3_epoch`, `n[k3_epoch & 1]`, `a`, `b`, `new_id`, `max_count` and `recount` are written
     // by the set-up step only, so every thread of every CTA of this launch reads the same values.
     if (!st->active) return;
@@ -815,14 +899,16 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
     auto snapshot = [&](uint32_t v) { return (v & TOKEN_MASK) == NW ? ((v & WORD_START_BIT) | A) : v; };
     const uint32_t AB = A | (B << 16);  // the low halves of a pair that may merge
 
-    // Start the copy of a tile: thread 0 issues the bulk copy, threads 32..35 fetch the edges.
-    // Callers make sure (barrier) that nobody still reads the buffer.
-    auto fetch_tile = [&](uint32_t tile) {
+
+    // Start the copy of a tile into buffer b: thread 0 issues the bulk copy, threads 32..35 fetch the
+    // edges.  Callers make sure (barrier) that nobody still reads the buffer.
+    auto fetch_tile = [&](uint32_t tile, uint32_t b) {
+        uint32_t* const in = mc_smem + b * BUF_WORDS + 4;
         const uint32_t i0 = tile * MC_TILE;
         if (threadIdx.x == 0) {
             const uint32_t bytes = ((min((uint32_t)MC_TILE, N - i0) + 3u) & ~3u) * 4u;
             fence_proxy_async_smem();
-            bulk_load(in, src + i0, bytes, &bar);
+            bulk_load(in, src + i0, bytes, &bar[b]);
         } else if (threadIdx.x == 32) {
             in[-1] = i0 > 0u ? src[i0 - 1u] : 0u;
         } else if (threadIdx.x >= 33 && threadIdx.x < 36) {
@@ -831,32 +917,52 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
         }
     };
 
+    // The tiles of a CTA go through two stages, one loop iteration apart:
+    //   stage 1 (turn j)      wait for the tile's bulk copy, pass 1, publish the tile's kept count, pass 2
+    //   stage 2 (turn j - 1)  look-back for the tile's offset, copy-out
+    // and the buffer that stage 2 frees takes the bulk copy of turn j + MC_NBUF - 1.  A tile's kept
+    // count is therefore published one whole iteration before the tile needs its own offset, and the
+    // time from taking a tile's ticket to publishing its count holds no wait on other tiles: a tile
+    // with a smaller number always publishes earlier (give or take the jitter of a bulk copy), so the
+    // look-back finds what it needs instead of waiting for the slowest of its predecessors.
     if (threadIdx.x == 0) {
-        mbar_init(&bar, 1u);
+#pragma unroll
+        for (int b = 0; b < MC_NBUF; b++) { mbar_init(&bar[b], 1u); s_tid[b] = 0xFFFFFFFFu; }
         fence_proxy_async_smem();
         s_fail = 0u;
         s_qcnt[0] = s_qcnt[1] = 0u;
-        s_tile = atomicAdd(&st->ticket, 1u);
+        // the first MC_NBUF - 1 tickets
+#pragma unroll
+        for (int b = 0; b < MC_NBUF - 1; b++) {
+            const uint32_t t = atomicAdd(&st->ticket, 1u);
+            s_tid[b] = t;
+            if (t >= ntiles) break;
+        }
     }
     __syncthreads();
-    uint32_t tile = s_tile;
-    uint32_t phase = 0u;
 #ifdef B200BPE_PHASES
     long long ph[8] = {0, 0, 0, 0, 0, 0, 0, 0}, ph_last = clock64();
 #endif
-    if (tile < ntiles) fetch_tile(tile);
-    while (tile < ntiles) {
-        if (threadIdx.x == 0) s_next = atomicAdd(&st->ticket, 1u);
+#pragma unroll
+    for (int b = 0; b < MC_NBUF - 1; b++)
+        if (s_tid[b] < ntiles) fetch_tile(s_tid[b], b);
+    uint32_t prev = 0xFFFFFFFFu;   // tile of the turn before (stage 2), if any
+    bool more = true;              // tickets below ntiles may still be had
+    for (uint32_t j = 0;; j++) {
+        const uint32_t cb = j % MC_NBUF, pb = (j + MC_NBUF - 1u) % MC_NBUF;   // buffers of turn j and of turn j - 1
+        const uint32_t tile = s_tid[cb];
+        if (tile >= ntiles && prev >= ntiles) break;
         PHASE_MARK(0);
-        if (!mbar_wait(&bar, phase)) s_fail = 1u;
-        phase ^= 1u;
-        __syncthreads();  // edges, next ticket and the failure flag visible
+        if (tile < ntiles && !mbar_wait(&bar[cb], (j / MC_NBUF) & 1u)) s_fail = 1u;
+        __syncthreads();  // edges and the failure flag visible
         PHASE_MARK(1);
         if (s_fail) {
             if (threadIdx.x == 0) atomicExch(&st->status, (uint32_t)DS_LOOKBACK_TIMEOUT);
             break;
         }
-        const uint32_t next = s_next;
+        uint32_t dec0 = 0u, dec1 = 0u, dec2 = 0u, dec3 = 0u;
+        if (tile < ntiles) {
+        uint32_t* const in = mc_smem + cb * BUF_WORDS + 4;
         const uint32_t tile0 = tile * MC_TILE;  // first symbol of the tile
 
         // ── pass 1: decide every symbol of the tile (kept? rewritten?) and count; nothing in the
@@ -868,8 +974,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
         //                  dropped and the one at k rewritten (train.wgsl:482-497)
         // so per row the decisions fit one byte (low nibble: own symbol kept, high nibble: own symbol
         // rewritten) and the four words of a tile stay in registers for pass 2.
-        uint32_t dec0 = 0u, dec1 = 0u, dec2 = 0u, dec3 = 0u;
-#pragma unroll 1
+        MC_UNROLL_SUBS
         for (int sub = 0; sub < MC_SUBS; sub++) {
             const uint32_t lw = sub * MC_SUB + warp * (MC_ROWS * 128);  // tile-local first symbol of the warp's span
             // a warp whose whole span (and the three symbols after it) lies below both N and the
@@ -898,7 +1003,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                 const uint32_t n2 = snapshot(in[lw + MC_ROWS * 128u + 2u]);
                 cand |= __byte_perm(n0, n1, 0x5410) == AB || __byte_perm(n1, n2, 0x5410) == AB;
             }
-            uint32_t kb = 0x0F0F0F0Fu, rew = 0u;   // per row one byte: own symbol kept (low nibble), rewritten (high nibble)
+            uint32_t kb = MC_KEEP_ALL, rew = 0u;   // per row one byte: own symbol kept (low nibble), rewritten (high nibble)
             if (!interior || __any_sync(0xFFFFFFFFu, cand)) {
             uint32_t L = 0u, R = 0u;
 #pragma unroll
@@ -925,13 +1030,13 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                 const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, L, 1), dn = __shfl_down_sync(0xFFFFFFFFu, R, 1);
                 const uint32_t l31 = __shfl_sync(0xFFFFFFFFu, L, 31), r0 = __shfl_sync(0xFFFFFFFFu, R, 0);
                 uint32_t pa = (up >> 4) & 0x01010101u, nb = (dn << 4) & 0x10101010u;
-                if (lane == 0) pa = ((l31 << 4) & 0x01010100u) | (e_prev & 1u);           // the row before, or the span's left edge
-                if (lane == 31) nb = ((r0 >> 4) & 0x00101010u) | ((e_n0 & 2u) << 27);     // the row after, or the span's right edge
+                if (lane == 0) pa = ((l31 << 4) & 0x01010100u & MC_ROWBYTES) | (e_prev & 1u);           // the row before, or the span's left edge
+                if (lane == 31) nb = ((r0 >> 4) & 0x00101010u & MC_NOTLAST) | ((e_n0 & 2u) << (MC_LASTROW_SHIFT + 3));     // the row after, or the span's right edge
                 L |= pa;
                 R |= nb;
             }
             uint32_t M = L & R;
-            kb = ~M & 0x0F0F0F0Fu;                     // own symbol t (t = 1..4) is dropped iff M[t-1]
+            kb = ~M & MC_KEEP_ALL;                     // own symbol t (t = 1..4) is dropped iff M[t-1]
             if (!interior) {
                 // live: bit 8j + k ↔ s[k] exists (k = 0: i0 >= 1; k >= 1: i0 + k - 1 < N); below: own symbol under the compaction limit
                 uint32_t live = 0u, below = 0u;
@@ -947,9 +1052,9 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                     below |= bl << (8 * j);
                 }
                 M &= live & (live >> 1);
-                kb = ~M & 0x0F0F0F0Fu & (live >> 1) & below;
+                kb = ~M & MC_KEEP_ALL & (live >> 1) & below;
             }
-            rew = (M >> 1) & 0x0F0F0F0Fu;              // and rewritten iff M[t]
+            rew = (M >> 1) & MC_KEEP_ALL;              // and rewritten iff M[t]
             const bool any_m = __any_sync(0xFFFFFFFFu, M != 0u);
             if (INCR && deltas) {
                 // The pair (t, t+1) changes iff one of the pairs at t-1, t, t+1 merges.  For lanes
@@ -957,12 +1062,12 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                 // has to look at the two pairs that begin after its right neighbour: the pairs
                 // (x, y) and (y, z) of the next row's lane 0, or of the symbols after the span.
                 const uint32_t m0 = __shfl_sync(0xFFFFFFFFu, M, 0);
-                uint32_t far = (m0 >> 8) & 0x00060606u;       // rows 0..2: bits 1, 2 of the next row's lane 0
+                uint32_t far = (m0 >> 8) & 0x00060606u & MC_NOTLAST;   // all rows but the last: bits 1, 2 of the next row's lane 0
                 {
                     const uint32_t i5 = tile0 + lw + MC_ROWS * 128u;  // index of the symbol after the span
                     const bool p1 = (e_n0 & 1u) && (e_n1 & 2u) && (interior || i5 + 1u < N);
                     const bool p2 = (e_n1 & 1u) && (e_n2 & 2u) && (interior || i5 + 2u < N);
-                    if (p1 || p2) far |= 0x02000000u;
+                    if (p1 || p2) far |= 0x02u << MC_LASTROW_SHIFT;
                 }
                 if (lane != 31) far = 0u;
                 if (any_m || __any_sync(0xFFFFFFFFu, far != 0u)) {
@@ -975,7 +1080,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                         uint32_t y = 0u, z = 0u;
                         if (lane == 0) s0 = snapshot(in[(int)l0 - 1]);
                         if (lane == 31) { s5 = snapshot(in[l0 + 4u]); y = snapshot(in[l0 + 5u]); z = snapshot(in[l0 + 6u]); }
-                        queue_deltas(st, table, dq, s_qcnt, s0, q[j], s5, y, z, tile0 + l0, N, interior, A, B, NW, lane, logC);
+                        queue_deltas(st, table, dq, s_qcnt, s0, q[j], s5, y, z, tile0 + l0, N, interior, A, B, NW, lane, logC, SHARD);
                     }
                 }
             }
@@ -1000,30 +1105,23 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
             }
             // kept symbols of the span
             uint32_t total = MC_ROWS * 128u;
-            if (__any_sync(0xFFFFFFFFu, kb != 0x0F0F0F0Fu)) {
+            if (__any_sync(0xFFFFFFFFu, kb != MC_KEEP_ALL)) {
                 uint32_t c = __popc(kb);
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, o);
                 total = c;
             }
-            if (lane == 0) span_cnt[sub * MC_WARPS + warp] = total;
+            if (lane == 0) span_cnt[cb][sub * MC_WARPS + warp] = total;
+        }
         }
         __syncthreads();  // the snapshot has been read by everybody; span counts visible
-        // offsets of the spans within the tile's output, and the tile's kept count
-        uint32_t span_off, span_cnt_reg, agg;
-        {
-            const uint32_t c = lane < MC_SUBS * MC_WARPS ? span_cnt[lane] : 0u;   // the spans of the tile, in tile order
-            span_cnt_reg = c;
-            uint32_t incl = c;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-                if (lane >= o) incl += t;
-            }
-            span_off = incl - c;
-            agg = __shfl_sync(0xFFFFFFFFu, incl, 31);
-        }
+        if (tile < ntiles) {
+        uint32_t* const in = mc_smem + cb * BUF_WORDS + 4;
         if (threadIdx.x == 0) {
+            // the tile's kept count, long before the tile needs its own offset
+            uint32_t agg = 0u;
+#pragma unroll
+            for (int k = 0; k < MC_SUBS * MC_WARPS; k++) agg += span_cnt[cb][k];
             const uint32_t flag = tile == 0u ? DESC_PREFIX : DESC_AGG;
             st_desc(desc + tile, ((unsigned long long)((tag << 2) | flag) << 32) | agg);
         }
@@ -1033,7 +1131,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
 #pragma unroll 1
         for (int sub = 0; sub < MC_SUBS; sub++) {
             const uint32_t d = sub == 0 ? dec0 : sub == 1 ? dec1 : sub == 2 ? dec2 : dec3;
-            if (__all_sync(0xFFFFFFFFu, d == 0x0F0F0F0Fu)) continue;
+            if (__all_sync(0xFFFFFFFFu, d == MC_KEEP_ALL)) continue;
             const uint32_t lw = sub * MC_SUB + warp * (MC_ROWS * 128);
             uint4 q[MC_ROWS];
 #pragma unroll
@@ -1066,31 +1164,68 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                 if (kb & 8u) in[o++] = v3;
             }
         }
+        }
         PHASE_MARK(3);
+        uint32_t next_ticket = 0xFFFFFFFFu;
+        if (prev < ntiles) {
+        const uint32_t tile = prev;
+        uint32_t* const in = mc_smem + pb * BUF_WORDS + 4;
+        // offsets of the spans within the tile's output, and the tile's kept count
+        uint32_t span_off, span_cnt_reg, agg;
+        {
+            const uint32_t c = lane < MC_SUBS * MC_WARPS ? span_cnt[pb][lane] : 0u;   // the spans of the tile, in tile order
+            span_cnt_reg = c;
+            uint32_t incl = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            span_off = incl - c;
+            agg = __shfl_sync(0xFFFFFFFFu, incl, 31);
+        }
 
-        // ── the tile's offset: look back over up to 256 predecessors per round, one warp per 32 ──
+        // ── the tile's offset: look back over up to 1,024 predecessors per round: every thread reads
+        // four descriptors (two 16-byte loads), nearest first, one warp per 128 ──
         uint32_t excl = 0u;
         if (tile != 0u) {
             int pos = (int)tile - 1;
             for (;;) {
-                const int idx = pos - (warp * 32 + lane);
-                uint32_t hi = (tag << 2) | DESC_PREFIX;  // positions before tile 0 act as a zero prefix
-                uint32_t val = 0u;
+                // this thread's descriptors: pos - 4 * t - k, k = 0..3, four independent loads in flight
+                const int base = pos - 4 * (warp * 32 + lane);
+                uint32_t hi[4], val[4];
                 bool timed_out = false;
                 for (uint32_t spins = 0;; spins++) {
-                    if (idx >= 0) {
-                        const unsigned long long dsc = ld_desc(desc + idx);
-                        hi = (uint32_t)(dsc >> 32);
-                        val = (uint32_t)dsc;
+                    bool ready = true;
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const int idx = base - k;
+                        hi[k] = (tag << 2) | DESC_PREFIX;   // positions before tile 0 act as a zero prefix
+                        val[k] = 0u;
+                        if (idx >= 0) {
+                            const unsigned long long dsc = ld_desc(desc + idx);
+                            hi[k] = (uint32_t)(dsc >> 32);
+                            val[k] = (uint32_t)dsc;
+                        }
+                        ready = ready && ((hi[k] >> 2) == tag) && (hi[k] & 3u) != 0u;
                     }
-                    const bool ready = ((hi >> 2) == tag) && (hi & 3u) != 0u;
                     if (__all_sync(0xFFFFFFFFu, ready)) break;
                     if (spins > LOOKBACK_MAX_SPINS) { timed_out = true; break; }
                     __nanosleep(20);
                 }
-                const uint32_t pmask = timed_out ? 1u : __ballot_sync(0xFFFFFFFFu, (hi & 3u) == DESC_PREFIX);
-                const int first = pmask ? (__ffs(pmask) - 1) : 32;  // nearest predecessor holding a full prefix
-                uint32_t contrib = (lane <= first && !timed_out) ? val : 0u;
+                // within the thread: add values, nearest first, up to and including the first full prefix
+                uint32_t mine = 0u;
+                bool mine_found = false;
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    if (!mine_found) {
+                        mine += val[k];
+                        mine_found = (hi[k] & 3u) == DESC_PREFIX;
+                    }
+                }
+                const uint32_t pmask = timed_out ? 1u : __ballot_sync(0xFFFFFFFFu, mine_found);
+                const int first = pmask ? (__ffs(pmask) - 1) : 32;  // nearest lane holding a full prefix
+                uint32_t contrib = (lane <= first && !timed_out) ? mine : 0u;
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xFFFFFFFFu, contrib, o);
                 if (lane == 0) {
@@ -1109,7 +1244,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                 }
                 __syncthreads();  // lb_sum / lb_found may be rewritten
                 if (found) break;
-                pos -= MC_THREADS;
+                pos -= 4 * MC_THREADS;
             }
         }
         if (threadIdx.x == 0) {
@@ -1131,7 +1266,11 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
         // a few single symbols bring the destination to a 16-byte boundary, then every store takes
         // its four words from two neighbouring 16-byte rows of the buffer.
         __syncwarp();  // the warp's own pass-2 writes are visible to all its lanes (tile 0 passes no barrier on the way here)
-#pragma unroll 1
+        // The next tile's ticket is taken only now, one copy-out before its load starts: a tile number
+        // that is reserved long before its tile is worked on makes every later tile wait in its
+        // look-back for a predecessor that has not even been loaded.
+        if (threadIdx.x == 0 && more) next_ticket = atomicAdd(&st->ticket, 1u);
+        MC_UNROLL_SUBS
         for (int sub = 0; sub < MC_SUBS; sub++) {
             const uint32_t lw = sub * MC_SUB + warp * (MC_ROWS * 128);
             const uint32_t cnt = __shfl_sync(0xFFFFFFFFu, span_cnt_reg, sub * MC_WARPS + warp);
@@ -1163,13 +1302,19 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
             const uint32_t done = head + 4u * nvec;
             if (done + lane < cnt) dst[off + done + lane] = sp[done + lane];
         }
-        __syncthreads();  // the buffer may be refilled
+        } else if (threadIdx.x == 0 && more) {
+            next_ticket = atomicAdd(&st->ticket, 1u);   // the first turn has nothing to copy out yet
+        }
+        // the buffer of turn j - 1 is free (or was never used): it takes the tile of turn j + MC_NBUF - 1
+        if (threadIdx.x == 0) s_tid[pb] = next_ticket;
+        __syncthreads();  // the buffer may be refilled; the new ticket is visible
         PHASE_MARK(5);
 #ifdef B200BPE_PHASES
         ph[6] += 1;
 #endif
-        tile = next;
-        if (tile < ntiles) fetch_tile(tile);
+        prev = tile;
+        const uint32_t nt = s_tid[pb];
+        if (nt < ntiles) fetch_tile(nt, pb); else more = false;
     }
     PHASE_MARK(7);
     if (INCR && deltas) {
@@ -1177,15 +1322,16 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
         // the updates commute with those of every other CTA, and doing it here, after the tiles,
         // keeps the scattered table traffic out of the streaming loop without another launch.
         __syncthreads();
-        apply_segment(st, dq, s_qcnt, blockIdx.x, table, logC);
+        apply_segment(st, dq, s_qcnt, blockIdx.x, table, logC, SHARD);
     }
     if (INCR && !deltas) {
         // a == b (or a rebuild is already due): no deltas were written, so nobody else touches the
         // table during this launch; empty it for the full count that the next merge starts with.
-        uint4* __restrict__ t4 = reinterpret_cast<uint4*>(table);
-        const uint32_t C = 1u << logC;
+        uint4* __restrict__ t4 = reinterpret_cast<uint4*>(SHARD ? st->owned : table);
+        const uint32_t C = 1u << (SHARD ? st->owned_log2 : logC);
         for (uint32_t i = blockIdx.x * MC_THREADS + threadIdx.x; i < C; i += gridDim.x * MC_THREADS)
             t4[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (SHARD && blockIdx.x == 0 && threadIdx.x == 0) st->owned_inserted = 0u;
     }
 #ifdef B200BPE_PHASES
     PHASE_MARK(7);

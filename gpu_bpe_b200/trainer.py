@@ -51,8 +51,9 @@ class TrainerSession:
         self._keep = []
 
     @staticmethod
-    def _opts(target_vocab_size, first_token_id, compat_mode, batch_merges, table_log2, flags):
+    def _opts(target_vocab_size, first_token_id, compat_mode, batch_merges, table_log2, flags, exchange_cap=0):
         o = _lib.TrainOpts()
+        o.exchange_cap = exchange_cap
         o.struct_size = C.sizeof(_lib.TrainOpts)
         o.target_vocab_size, o.first_token_id = target_vocab_size, first_token_id
         o.batch_merges, o.table_log2, o.flags = batch_merges, table_log2, flags
@@ -62,8 +63,8 @@ class TrainerSession:
     @classmethod
     def create(cls, engine, data: np.ndarray, word_starts, *, target_vocab_size=4096, first_token_id=256,
                compat_mode="literal", batch_merges=BATCH_SIZE, table_log2=0, flags=0, device_pointers=False,
-               n: int | None = None):
-        o = cls._opts(target_vocab_size, first_token_id, compat_mode, batch_merges, table_log2, flags)
+               n: int | None = None, exchange_cap=0):
+        o = cls._opts(target_vocab_size, first_token_id, compat_mode, batch_merges, table_log2, flags, exchange_cap)
         h = C.c_void_p()
         L = _lib.lib()
         if device_pointers:
@@ -123,6 +124,18 @@ class TrainerSession:
         _lib.check(_lib.lib().b200bpe_trainer_kernel_stats(self._h, C.byref(ks)))
         return {f: getattr(ks, f) for f, _ in _lib.KernelStats._fields_}
 
+    def launches(self) -> int:
+        """Kernel launches of this trainer since it was created (a graph launch counts its kernels)."""
+        n = C.c_uint64()
+        _lib.check(_lib.lib().b200bpe_trainer_launches(self._h, C.byref(n)))
+        return n.value
+
+    def exchange_kind(self) -> str:
+        """'none' (one GPU), 'peer' (this library's kernels over NVLink peer memory) or 'nccl'."""
+        k = C.c_uint32()
+        _lib.check(_lib.lib().b200bpe_trainer_exchange_kind(self._h, C.byref(k)))
+        return ("none", "peer", "nccl")[k.value]
+
     def last_run_ms(self) -> float:
         ms = C.c_double()
         _lib.check(_lib.lib().b200bpe_trainer_last_run_ms(self._h, C.byref(ms)))
@@ -159,16 +172,6 @@ class BPETrainer:
         out = np.zeros((merges_needed, 3), np.uint32)
         n, es = C.c_uint32(), C.c_uint32()
         vocab = self._vocab
-
-        def _cb(p, _u):
-            if onProgress:
-                p = p.contents
-                last = (vocab.entries[p.last_a] + vocab.entries[p.last_b]) if p.last_count else None
-                from .vocab import bytes_to_display_string
-                onProgress({"mergeIndex": p.merge_index, "totalMerges": p.total_merges,
-                            "mergeString": bytes_to_display_string(last) if last else "—",
-                            "bestCount": p.last_count, "symbolCount": p.symbol_count,
-                            "mergesPerSecond": p.merges_per_second})
 
         # The progress payload needs the merged string, so the vocabulary is extended per batch
         # inside the callback path: entries for ids below last_new_id are added lazily.

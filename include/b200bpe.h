@@ -51,9 +51,13 @@ enum {
 enum {
     B200BPE_FLAG_NO_GRAPH = 1u,      /* launch kernels one by one instead of one CUDA graph per batch */
     B200BPE_FLAG_TIME_KERNELS = 2u,  /* bracket every kernel with CUDA events (implies NO_GRAPH) */
-    B200BPE_FLAG_FULL_RECOUNT = 4u   /* rebuild the pair table with a full count before every merge, as the
+    B200BPE_FLAG_FULL_RECOUNT = 4u,  /* rebuild the pair table with a full count before every merge, as the
                                         reference does (train.wgsl:196-202,376-431), instead of updating it in
                                         place around the merged occurrences; the merge list is the same */
+    B200BPE_FLAG_NCCL_EXCHANGE = 8u  /* sharded runs: exchange the pair counts with NCCL send/recv and all-reduce
+                                        instead of this library's own kernels over NVLink peer memory (the default,
+                                        which needs one process per GPU and CUDA IPC between them; the library falls
+                                        back to NCCL by itself when the peers' buffers cannot be mapped) */
 };
 
 typedef struct b200bpe_ctx b200bpe_ctx;
@@ -69,7 +73,8 @@ typedef struct {
     uint32_t compat_mode;       /* B200BPE_COMPAT_* (default LITERAL on one GPU; FIXED is required when sharded) */
     uint32_t table_log2;        /* log2 of the pair-table capacity in slots; 0 = sized from the corpus, grows on demand */
     uint32_t flags;             /* B200BPE_FLAG_* */
-    uint32_t reserved;
+    uint32_t exchange_cap;      /* tests only: first bucket size of the NCCL exchange in slots (0 = default), to reach
+                                   the bucket-overflow path with a small corpus */
 } b200bpe_train_opts;
 
 /* Progress payload, one call per batch: the fields of trainer.js:306-314. */
@@ -148,6 +153,11 @@ b200bpe_status b200bpe_trainer_symbols(b200bpe_trainer*, uint32_t* out, uint64_t
 b200bpe_status b200bpe_trainer_pair_counts(b200bpe_trainer*, uint64_t* keys_out, uint32_t* counts_out, uint64_t cap,
                                            uint64_t* n_distinct_out);
 b200bpe_status b200bpe_trainer_kernel_stats(b200bpe_trainer*, b200bpe_kernel_stats* out);
+/* Kernels this trainer has launched since it was created (a graph launch counts the kernels it holds);
+ * and which count exchange a sharded trainer uses: 0 none (one GPU), 1 peer memory, 2 NCCL.  Diagnostics;
+ * no counterpart in the reference. */
+b200bpe_status b200bpe_trainer_launches(b200bpe_trainer*, uint64_t* n_out);
+b200bpe_status b200bpe_trainer_exchange_kind(b200bpe_trainer*, uint32_t* kind_out);
 /* Milliseconds of device time of the last b200bpe_trainer_run, by CUDA events on the library's stream. */
 b200bpe_status b200bpe_trainer_last_run_ms(b200bpe_trainer*, double* ms);
 /* Milliseconds of device time of the last b200bpe_trainer_reset (symbol tagging and buffer clears). */

@@ -1,7 +1,8 @@
-"""Worker of the multi-GPU parity test: run under torch.distributed.run, one rank per GPU.
+"""Worker of the multi-GPU parity tests: run under torch.distributed.run, one rank per GPU.
 
 Every rank builds the same seeded corpus, keeps its word-aligned span, trains jointly, and rank 0
 checks the merge list, the gathered symbols and the exchanged pair counts against the CPU oracle.
+Options come through B200BPE_TEST_* environment variables set by tests/test_multi_gpu.py.
 """
 import os
 import sys
@@ -15,7 +16,7 @@ sys.path.insert(0, ROOT)
 
 
 def main():
-    from gpu_bpe_b200 import BPEEngine, TrainerSession, TrieTokenizer
+    from gpu_bpe_b200 import BPEEngine, TrainerSession, TrieTokenizer, _lib
     from gpu_bpe_b200.sharding import document_cuts, word_aligned_cuts
     from gpu_bpe_b200 import synth
     from oracle import cpu_oracle as O
@@ -25,8 +26,19 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    merges = int(os.environ.get("B200BPE_TEST_MERGES", "300"))
-    data, mask, sym = small_text(2, 41, 4 << 20)
+    env = os.environ.get
+    merges = int(env("B200BPE_TEST_MERGES", "300"))
+    exchange = env("B200BPE_TEST_EXCHANGE", "peer")
+    first_cap = int(env("B200BPE_TEST_EXCHANGE_CAP", "0"))
+    table_log2 = int(env("B200BPE_TEST_TABLE_LOG2", "0"))
+    batch = int(env("B200BPE_TEST_BATCH", "128"))
+    data, mask, sym = small_text(2, 41, int(env("B200BPE_TEST_CORPUS_KIB", "4096")) << 10)
+    if env("B200BPE_TEST_ONE_WORD"):
+        # one single word: every cut but the first falls at the end, so the other ranks' spans are empty
+        data = np.frombuffer(b"abcabcabcabdabcabdabcabcabd" * 40, np.uint8).copy()
+        mask = np.zeros(data.size, np.uint8)
+        mask[0] = 1
+        sym = data.astype(np.uint32) | (mask.astype(np.uint32) << 16)
     cuts = word_aligned_cuts(mask, world)
     lo, hi = int(cuts[rank]), int(cuts[rank + 1])
 
@@ -34,15 +46,19 @@ def main():
     dist.broadcast_object_list(uid, src=0)
     engine = BPEEngine(local).init_distributed(rank, world, uid[0])
 
-    s = TrainerSession.create(engine, data[lo:hi], mask[lo:hi], target_vocab_size=256 + merges, compat_mode="fixed")
+    s = TrainerSession.create(engine, data[lo:hi], mask[lo:hi], target_vocab_size=256 + merges, compat_mode="fixed",
+                              flags=_lib.FLAG_NCCL_EXCHANGE if exchange == "nccl" else 0, exchange_cap=first_cap,
+                              table_log2=table_log2, batch_merges=batch)
+    kind = s.exchange_kind()
+    assert kind == exchange, f"asked for the {exchange} exchange, got {kind}"
     # exchanged counts before any merge: the union of the ranks' owned partitions is the global histogram
-    # (with buckets forced far too small the one-shot count exchange gives up by design; the run resizes them)
-    tiny = "B200BPE_EXCHANGE_CAP" in os.environ
+    # (with buckets or tables forced far too small the one-shot count exchange gives up by design; the run resizes them)
+    tiny = bool(first_cap) or bool(table_log2)
     mine = {} if tiny else s.pair_counts()
     parts = [None] * world
     dist.all_gather_object(parts, mine)
-    # first half, then the exchanged counts of the half-trained corpus (the local tables are kept up
-    # to date by the merge kernel by now and must survive being read), then the rest
+    # first half, then the exchanged counts of the half-trained corpus (kept up to date by the merge
+    # kernels by now; they must survive being read), then the rest
     m1, c1, _ = s.run(merges // 2)
     mid_counts = {} if tiny else s.pair_counts()
     mid_syms = s.symbols().copy()
@@ -55,6 +71,10 @@ def main():
     dist.all_gather_object(finals, final)
     lists = [None] * world
     dist.all_gather_object(lists, np.concatenate([m, c[:, None]], axis=1).tolist())
+    # a reset puts everything back: the second run gives the same list
+    s.reset()
+    m3, c3, _ = s.run()
+    assert np.array_equal(m3, m) and np.array_equal(c3, c), "a run after reset differs"
     s.destroy()
 
     # encoding shards documents; no collective on the data path
@@ -69,7 +89,6 @@ def main():
     chunk = tok.chunkSize
     tok.destroy()
 
-    ok = True
     if rank == 0:
         want = O.train(sym, merges, "fixed", threads=8)
         assert all(l == lists[0] for l in lists), "ranks disagree on the merge list"
@@ -95,7 +114,7 @@ def main():
                 k = d - int(dc[r])
                 ref = O.encode(data[a:b], trie, chunk) if b > a else np.zeros(0, np.uint32)
                 assert np.array_equal(t[int(to[k]):int(to[k + 1])], ref), f"document {d} differs"
-        print(f"multi-gpu ok: world={world} merges={len(lists[0])} early={early}", flush=True)
+        print(f"multi-gpu ok: world={world} exchange={kind} merges={len(lists[0])} early={early}", flush=True)
     dist.barrier()
     engine.destroy()
     dist.destroy_process_group()
