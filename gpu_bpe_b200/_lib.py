@@ -128,6 +128,8 @@ def synth():
         S = C.CDLL(SYNTH_PATH)
         S.b200bpe_synth_corpus.argtypes = [C.c_int, C.c_uint64, C.c_uint64, C.c_void_p, C.c_int]
         S.b200bpe_synth_corpus.restype = C.c_int
+        S.b200bpe_synth_corpus_range.argtypes = [C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p, C.c_int]
+        S.b200bpe_synth_corpus_range.restype = C.c_int
         S.b200bpe_synth_doc_offsets.argtypes = [C.c_uint64, C.c_uint64, C.c_uint32, C.c_double, C.c_void_p]
         S.b200bpe_synth_doc_offsets.restype = C.c_int
         _synth = S

@@ -3,7 +3,8 @@
     python -m gpu_bpe_b200.build [--force]
 
 Produces gpu_bpe_b200/libb200bpe.so (nvcc, CUDA runtime linked statically, NCCL resolved at run
-time with dlopen) and gpu_bpe_b200/libb200bpe_synth.so (g++).  nvcc cross-compiles without a GPU.
+time with dlopen) and gpu_bpe_b200/libb200bpe_synth.so (g++: synthetic corpora and the host
+pre-tokeniser, no CUDA).  nvcc cross-compiles without a GPU.
 """
 from __future__ import annotations
 
@@ -40,9 +41,11 @@ def build(force: bool = False, verbose: bool = False) -> tuple[str, str]:
         srcs = [os.path.join(CSRC, f) for f in CUDA_SOURCES if os.path.exists(os.path.join(CSRC, f))]
         cmd = ["nvcc", *NVCC_FLAGS, *( ["-Xptxas", "-v"] if verbose else []), *srcs, "-o", LIB, "-ldl"]
         subprocess.check_call(cmd)
-    if force or not _newer(SYNTH, [os.path.join(CSRC, "synth.cpp")]):
-        subprocess.check_call(["g++", "-std=c++17", "-O2", "-shared", "-fPIC", "-pthread",
-                               os.path.join(CSRC, "synth.cpp"), "-o", SYNTH])
+    # host-only helpers (no CUDA): the synthetic corpora and the host pre-tokeniser, for callers that
+    # must not load the CUDA library (the CPU arm of the benchmark)
+    host_srcs = [os.path.join(CSRC, f) for f in ("synth.cpp", "pretok.cpp")]
+    if force or not _newer(SYNTH, host_srcs + [os.path.join(CSRC, "unicode_classes.inc")]):
+        subprocess.check_call(["g++", "-std=c++17", "-O2", "-shared", "-fPIC", "-pthread", *host_srcs, "-o", SYNTH])
     return LIB, SYNTH
 
 

@@ -190,8 +190,12 @@ extern "C" {
 // kind 1: ASCII (20,000-word lexicon, Zipf 1.1, numbers and punctuation, newline about every 80 bytes).
 // kind 2: UTF-8 mix (50,000 words per script, Zipf 1.1, lognormal lines).
 // kind 5: kind 2 with Zipf 1.0 over 500,000 words plus random base64-like strings.
-int b200bpe_synth_corpus(int kind, uint64_t seed, uint64_t n_bytes, uint8_t* out, int threads) {
-    if (!out || (kind != 1 && kind != 2 && kind != 5)) return 1;
+// Bytes [offset, offset + len) of the corpus of n_bytes bytes: the same bytes as the whole corpus
+// holds there (blocks are independent), so every rank of a sharded job can make just its span.
+int b200bpe_synth_corpus_range(int kind, uint64_t seed, uint64_t n_bytes, uint64_t offset, uint64_t len, uint8_t* out,
+                               int threads) {
+    if ((!out && len) || (kind != 1 && kind != 2 && kind != 5) || offset > n_bytes || len > n_bytes - offset) return 1;
+    if (len == 0) return 0;
     Plan P;
     P.kind = kind;
     if (kind == 1) {
@@ -204,19 +208,31 @@ int b200bpe_synth_corpus(int kind, uint64_t seed, uint64_t n_bytes, uint8_t* out
         P.cjk = make_cjk(seed ^ 0x33, nwords, z);
     }
     const uint64_t B = 1ull << 20;
-    const uint64_t blocks = (n_bytes + B - 1) / B;
-    const int T = std::max(1, std::min<int>(threads, (int)std::max<uint64_t>(1, blocks)));
+    const uint64_t b0 = offset / B, b1 = (offset + len + B - 1) / B;   // blocks [b0, b1)
+    const int T = std::max(1, std::min<int>(threads, (int)(b1 - b0)));
     std::vector<std::thread> pool;
     for (int t = 0; t < T; t++) {
         pool.emplace_back([&, t]() {
-            for (uint64_t b = t; b < blocks; b += T) {
-                const uint64_t lo = b * B, len = std::min(B, n_bytes - lo);
-                make_block(P, seed, b, out + lo, (size_t)len);
+            std::vector<uint8_t> tmp;
+            for (uint64_t b = b0 + t; b < b1; b += T) {
+                const uint64_t lo = b * B, blen = std::min(B, n_bytes - lo);
+                const uint64_t from = std::max(lo, offset), to = std::min(lo + blen, offset + len);
+                if (from == lo && to == lo + blen) {
+                    make_block(P, seed, b, out + (lo - offset), (size_t)blen);
+                } else {
+                    tmp.resize(blen);
+                    make_block(P, seed, b, tmp.data(), (size_t)blen);
+                    std::memcpy(out + (from - offset), tmp.data() + (from - lo), (size_t)(to - from));
+                }
             }
         });
     }
     for (auto& th : pool) th.join();
     return 0;
+}
+
+int b200bpe_synth_corpus(int kind, uint64_t seed, uint64_t n_bytes, uint8_t* out, int threads) {
+    return b200bpe_synth_corpus_range(kind, seed, n_bytes, 0, n_bytes, out, threads);
 }
 
 // Cut n_bytes into n_docs documents with lognormal lengths (sigma given, mean n_bytes / n_docs).

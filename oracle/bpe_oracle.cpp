@@ -194,11 +194,26 @@ void oracle_word_boundary(uint32_t* sym, uint64_t n) {
 
 // Exact pair histogram of sym[0..n): writes up to cap (key, count) entries sorted by key,
 // returns the number of distinct pairs (which may exceed cap).
+uint64_t oracle_pair_counts_mt(const uint32_t* sym, uint64_t n, uint32_t* keys_out, uint32_t* counts_out,
+                               uint64_t cap, int threads);
+
 uint64_t oracle_pair_counts(const uint32_t* sym, uint64_t n, uint32_t* keys_out, uint32_t* counts_out,
                             uint64_t cap) {
-    CountTable tb(1u << 16);
-    uint32_t key;
-    for (uint64_t id = 0; id < n; id++) if (pair_at(sym, id, n, &key)) tb.add(key, 1);
+    return oracle_pair_counts_mt(sym, n, keys_out, counts_out, cap, 1);
+}
+
+// The same histogram with the positions split over `threads` threads (private tables, then summed).
+uint64_t oracle_pair_counts_mt(const uint32_t* sym, uint64_t n, uint32_t* keys_out, uint32_t* counts_out,
+                               uint64_t cap, int threads) {
+    const int T = (threads <= 1 || n < 4096) ? 1 : threads;
+    std::vector<CountTable> part(T, CountTable(1u << 16));
+    parallel_for(T, n, [&](int t, uint64_t lo, uint64_t hi) {
+        uint32_t key;
+        for (uint64_t id = lo; id < hi; id++) if (pair_at(sym, id, n, &key)) part[t].add(key, 1);
+    });
+    CountTable& tb = part[0];
+    for (int t = 1; t < T; t++)
+        for (size_t i = 0; i < part[t].keys.size(); i++) if (part[t].keys[i]) tb.add(part[t].keys[i], part[t].vals[i]);
     std::vector<std::pair<uint32_t, uint32_t>> v;
     for (size_t i = 0; i < tb.keys.size(); i++) if (tb.keys[i]) v.push_back({tb.keys[i], tb.vals[i]});
     std::sort(v.begin(), v.end());
@@ -364,6 +379,55 @@ uint64_t oracle_encode(const uint8_t* bytes, uint64_t n, const uint8_t* trie, ui
             for (size_t i = 0; i < toks[t].size() && total + i < cap; i++) tokens_out[total + i] = toks[t][i];
         total += toks[t].size();
     }
+    return total;
+}
+
+// Many documents, each encoded as a separate call of oracle_encode would encode it (chunks are
+// counted from the document's first byte).  doc_offsets has n_docs + 1 entries into bytes;
+// tok_offsets_out (n_docs + 1 entries) receives where each document's tokens start in tokens_out.
+// Threads take contiguous runs of documents.  Returns the number of tokens, or UINT64_MAX on a bad trie.
+uint64_t oracle_encode_batch(const uint8_t* bytes, const uint64_t* doc_offsets, uint32_t n_docs, const uint8_t* trie,
+                             uint64_t trie_len, uint32_t chunk_size, int threads, uint32_t* tokens_out, uint64_t cap,
+                             uint64_t* tok_offsets_out) {
+    const int T = std::max(1, std::min<int>(threads, (int)std::max<uint32_t>(1, n_docs)));
+    std::vector<std::vector<uint32_t>> toks(T);
+    std::vector<std::vector<uint64_t>> lens(T);
+    std::vector<uint32_t> first(T + 1, n_docs);
+    const uint64_t total_bytes = doc_offsets[n_docs] - doc_offsets[0];
+    first[0] = 0;
+    for (int t = 1; t < T; t++) {   // balance by bytes
+        const uint64_t want = doc_offsets[0] + total_bytes / T * t;
+        uint32_t d = first[t - 1];
+        while (d < n_docs && doc_offsets[d] < want) d++;
+        first[t] = d;
+    }
+    std::atomic<int> bad{0};
+    std::vector<std::thread> pool;
+    for (int t = 0; t < T; t++) {
+        pool.emplace_back([&, t]() {
+            std::vector<uint32_t> tmp;
+            for (uint32_t d = first[t]; d < first[t + 1]; d++) {
+                const uint64_t a = doc_offsets[d], b = doc_offsets[d + 1];
+                tmp.resize(std::max<uint64_t>(1, b - a));
+                const uint64_t k = b > a ? oracle_encode(bytes + a, b - a, trie, trie_len, chunk_size, 1, tmp.data(), tmp.size()) : 0;
+                if (k == UINT64_MAX) { bad = 1; return; }
+                toks[t].insert(toks[t].end(), tmp.begin(), tmp.begin() + k);
+                lens[t].push_back(k);
+            }
+        });
+    }
+    for (auto& th : pool) th.join();
+    if (bad) return UINT64_MAX;
+    uint64_t total = 0;
+    uint32_t d = 0;
+    for (int t = 0; t < T; t++) {
+        uint64_t local = 0;
+        for (uint64_t k : lens[t]) { tok_offsets_out[d++] = total + local; local += k; }
+        if (tokens_out)
+            for (size_t i = 0; i < toks[t].size() && total + i < cap; i++) tokens_out[total + i] = toks[t][i];
+        total += toks[t].size();
+    }
+    tok_offsets_out[n_docs] = total;
     return total;
 }
 

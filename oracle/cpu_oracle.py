@@ -25,6 +25,10 @@ def lib():
         L.oracle_word_boundary.restype = None
         L.oracle_pair_counts.argtypes = [u32p, C.c_uint64, u32p, u32p, C.c_uint64]
         L.oracle_pair_counts.restype = C.c_uint64
+        L.oracle_pair_counts_mt.argtypes = [u32p, C.c_uint64, u32p, u32p, C.c_uint64, C.c_int]
+        L.oracle_pair_counts_mt.restype = C.c_uint64
+        L.oracle_encode_batch.argtypes = [u8p, u64p, C.c_uint32, u8p, C.c_uint64, C.c_uint32, C.c_int, u32p, C.c_uint64, u64p]
+        L.oracle_encode_batch.restype = C.c_uint64
         L.oracle_train.argtypes = [u32p, C.c_uint64, C.c_uint32, C.c_int, C.c_uint32, C.c_int, C.c_double,
                                    u32p, u32p, u32p, u32p, u64p, C.POINTER(C.c_double)]
         L.oracle_train.restype = C.c_int
@@ -52,13 +56,13 @@ def word_boundary(byte_values: np.ndarray) -> np.ndarray:
     return sym
 
 
-def pair_counts(sym: np.ndarray) -> dict[int, int]:
+def pair_counts(sym: np.ndarray, threads: int = 1) -> dict[int, int]:
     sym = np.ascontiguousarray(sym, dtype=np.uint32)
     cap = 1 << 16
     while True:
         k = np.empty(cap, np.uint32)
         v = np.empty(cap, np.uint32)
-        n = lib().oracle_pair_counts(_p(sym, C.c_uint32), sym.size, _p(k, C.c_uint32), _p(v, C.c_uint32), cap)
+        n = lib().oracle_pair_counts_mt(_p(sym, C.c_uint32), sym.size, _p(k, C.c_uint32), _p(v, C.c_uint32), cap, threads)
         if n <= cap:
             return dict(zip(k[:n].tolist(), v[:n].tolist()))
         cap = int(n)
@@ -89,6 +93,21 @@ def encode(data: np.ndarray, trie: bytes, chunk_size: int, threads: int = 1) -> 
     if n == 2**64 - 1:
         raise ValueError("bad trie")
     return out[:n].copy()
+
+
+def encode_batch(data: np.ndarray, doc_offsets: np.ndarray, trie: bytes, chunk_size: int, threads: int = 1):
+    """Every document encoded as its own encode() call → (tokens, token offsets per document)."""
+    data = np.ascontiguousarray(data, dtype=np.uint8)
+    offs = np.ascontiguousarray(doc_offsets, dtype=np.uint64)
+    tb = np.frombuffer(trie, dtype=np.uint8)
+    cap = max(1, int(offs[-1] - offs[0]))
+    out = np.empty(cap, np.uint32)
+    toff = np.zeros(offs.size, np.uint64)
+    n = lib().oracle_encode_batch(_p(data, C.c_uint8), _p(offs, C.c_uint64), offs.size - 1, _p(tb, C.c_uint8), tb.size,
+                                  chunk_size, threads, _p(out, C.c_uint32), cap, _p(toff, C.c_uint64))
+    if n == 2**64 - 1:
+        raise ValueError("bad trie")
+    return out[:n].copy(), toff
 
 
 def train_words(sym_or_bytes: np.ndarray, max_merges: int, word_starts: np.ndarray | None = None, first_id: int = 256,
