@@ -503,7 +503,7 @@ def main():
                   "workload": f"config4: {ENCODE_BYTES // MIB} MiB synthetic UTF-8 (seed {ENCODE_SEED}) in {ENCODE_DOCS} lognormal documents, "
                               f"{len(vocab.entries)}-entry vocabulary (the merge list of config 3), chunk {tok.chunkSize}",
                   "trie": {"nodes": tok.nodeCount, "edges": tok.edgeCount, "max_token_len": tok.maxTokenLen,
-                           "layout": "shared-memory cuckoo table" if sub.value else "global hash table behind a probe cache",
+                           "layout": {0: "global hash table behind a probe cache", 1: "hybrid: hot transitions in shared memory, two-byte first step"}.get(sub.value, "shared-memory cuckoo table"),
                            "log2_slots": lg.value},
                   "tokens": tot_tok, "walk_ms": w_ms, "scan_compact_ms": c_ms, "scaling": "strong",
                   "e2e_GB_per_s": ENCODE_BYTES / 1e9 / (float(np.mean(e_ms)) / 1e3),

@@ -28,6 +28,14 @@ class TrainOpts(C.Structure):
                 ("flags", C.c_uint32), ("exchange_cap", C.c_uint32)]
 
 
+class TokOpts(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("chunk_size", C.c_uint32), ("layout", C.c_uint32), ("reserved", C.c_uint32),
+                ("batch_slice_bytes", C.c_uint64), ("encode_slice_bytes", C.c_uint64)]
+
+
+TRIE_LAYOUTS = {"auto": 0, "cuckoo": 1, "hybrid": 2, "hash": 3}
+
+
 class Progress(C.Structure):
     _fields_ = [("merge_index", C.c_uint32), ("total_merges", C.c_uint32), ("last_a", C.c_uint32),
                 ("last_b", C.c_uint32), ("last_new_id", C.c_uint32), ("last_count", C.c_uint32),
@@ -77,6 +85,7 @@ SIGNATURES = {
     "b200bpe_trie_compile": (C.c_int32, [C.c_void_p, u64p, C.c_uint32, C.c_void_p, C.POINTER(C.c_size_t)]),
     "b200bpe_trie_parse_header": (C.c_int32, [C.c_void_p, C.c_size_t, u32p]),
     "b200bpe_tokenizer_create": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_uint32, C.POINTER(C.c_void_p)]),
+    "b200bpe_tokenizer_create_ex": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_size_t, C.POINTER(TokOpts), C.POINTER(C.c_void_p)]),
     "b200bpe_tokenizer_info": (C.c_int32, [C.c_void_p, u32p, u32p, u32p, u32p]),
     "b200bpe_tokenizer_layout": (C.c_int32, [C.c_void_p, u32p, u32p]),
     "b200bpe_encode": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64, u64p]),

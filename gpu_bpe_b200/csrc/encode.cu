@@ -13,6 +13,14 @@
 //     4-byte entries that every CTA copies into its shared memory.  The 24-bit key is permuted by
 //     an odd multiplier modulo 2^24; the top bits pick the slot and only the rest is stored next to
 //     the 18-bit packed child, so a lookup is two or three shared-memory loads and no branch
+//   * medium tries (every index below 130,816; the 32,256-entry vocabulary of the benchmark has
+//     86 K nodes): a HYBRID.  The walk's first step takes TWO bytes at once: the pairs (b0, b1)
+//     that lead to a depth-2 node are keyed like transitions of a pseudo parent, and a 256-entry
+//     table of the root's children says what a single byte is worth.  These and the most used of
+//     the deeper transitions (ranked by the smallest token id below them: token ids are merge
+//     ranks, so small means frequent) fill a bucketed cuckoo table in shared memory (two
+//     sub-tables, buckets of two 4-byte entries, one 8-byte load each); the rest stay in a global
+//     table, and a bit per node says whether a miss in shared memory has to look there at all
 //   * larger tries: an open-addressing table of 8-byte entries in global memory, at most half
 //     full, pinned in L2 with an access-policy window, behind a direct-mapped shared-memory cache
 //     of recent probes (hits and misses) per CTA
@@ -42,6 +50,27 @@ constexpr int CK_THREADS = 1024;   // cuckoo walk: one CTA per SM, the whole tab
 constexpr uint32_t CK_MIN_LOG2 = 11, CK_MAX_LOG2 = 14;  // slots per sub-table
 constexpr uint32_t CK_HAS_TOKEN = 1u << 16, CK_LEAF = 1u << 17, CK_INDEX = 0xFFFFu, CK_VALUE = 0x3FFFFu;
 constexpr uint32_t CK_EMPTY = 0xFFFFFFFFu;
+
+// hybrid layout: 4-byte entries  remainder(13) << 19 | leaf << 18 | has_token << 17 | index(17)
+constexpr int HY_THREADS = 512;
+constexpr int HY_CTAS = 3;
+constexpr uint32_t HY_BUCKET_LOG2 = 12;                       // buckets per sub-table; a bucket holds two entries
+constexpr uint32_t HY_KEY_BITS = 25, HY_KEY_MASK = (1u << HY_KEY_BITS) - 1u;
+constexpr uint32_t HY_REM_SHIFT = HY_KEY_BITS - HY_BUCKET_LOG2;   // 13 remainder bits
+constexpr uint32_t HY_INDEX = 0x1FFFFu, HY_HAS_TOKEN = 1u << 17, HY_LEAF = 1u << 18;
+constexpr uint32_t HY_ROOT2 = 0x1FF00u;                       // pseudo parents 0x1FF00 | b0 of the two-byte first step
+constexpr uint32_t HY_MAX_INDEX = HY_ROOT2;                   // real node indices stay below
+constexpr uint32_t HY_HOT_WORDS = 2u * (1u << HY_BUCKET_LOG2) * 2u;   // 16,384 entries = 64 KB
+constexpr uint32_t HY_SMEM_BYTES = HY_HOT_WORDS * 4u + 256u * 4u;
+constexpr double HY_MAX_LOAD = 0.86;
+
+struct TrieHybrid {
+    const uint32_t* hot;     // two sub-tables of (1 << HY_BUCKET_LOG2) buckets of two entries, then the 256 root children
+    uint32_t mul[2];         // odd multipliers of the two hash functions (modulo 2^25)
+    const uint2* cold;       // open addressing: {key, value in the 4-byte entry's value format}
+    uint32_t cold_mask;
+    const uint32_t* cold_bits;  // bit per node index: some child of the node is only in the cold table
+};
 
 struct TrieDev {
     const uint2* trans;      // {parent << 8 | byte, packed child}
@@ -213,6 +242,113 @@ k_trie_walk(TrieDev t, const uint8_t* __restrict__ bytes, uint64_t n, uint32_t c
             if (k > 0u) out[base] = buf.x;
             if (k > 1u) out[base + 1] = buf.y;
             if (k > 2u) out[base + 2] = buf.z;
+        }
+        counts[g] = tw;
+    }
+}
+
+// The hybrid walk.  One thread per chunk, one flat loop; an iteration is one probe of the shared
+// table.  In the first iteration of a token the probe takes two bytes (key: pseudo parent of the
+// first byte, second byte) and the root's child table gives the one-byte candidate; a miss there
+// ends the token at once.  Later iterations take one byte.  Tokens are stored as they end.
+__global__ void __launch_bounds__(HY_THREADS, HY_CTAS)
+k_trie_walk_hybrid(TrieHybrid t, const uint8_t* __restrict__ bytes, uint64_t n, uint32_t cs, const uint64_t* __restrict__ doc_off,
+                   const uint64_t* __restrict__ chunk_base, uint32_t n_docs, uint64_t n_chunks_static,
+                   uint32_t* __restrict__ staging, uint32_t* __restrict__ counts, uint32_t* __restrict__ ticket) {
+    extern __shared__ __align__(16) unsigned char tw_smem[];
+    uint32_t* sm = reinterpret_cast<uint32_t*>(tw_smem);
+    {
+        const uint4* __restrict__ src = reinterpret_cast<const uint4*>(t.hot);
+        for (uint32_t i = threadIdx.x; i < HY_SMEM_BYTES / 16u; i += HY_THREADS) reinterpret_cast<uint4*>(tw_smem)[i] = __ldg(src + i);
+    }
+    __syncthreads();
+    const uint2* __restrict__ hot0 = reinterpret_cast<const uint2*>(sm);
+    const uint2* __restrict__ hot1 = hot0 + (1u << HY_BUCKET_LOG2);
+    const uint32_t* __restrict__ t1 = sm + HY_HOT_WORDS;
+    const uint32_t mul0 = t.mul[0], mul1 = t.mul[1];
+    const uint64_t n_chunks = doc_off ? chunk_base[n_docs] : n_chunks_static;
+    const uint32_t shift = (uint32_t)(reinterpret_cast<uintptr_t>(bytes) & 3u);
+    const uint32_t* __restrict__ words = reinterpret_cast<const uint32_t*>(reinterpret_cast<uintptr_t>(bytes) - shift);
+    const uint64_t last_word = (n + shift + 3u) / 4u;   // words [0, last_word) hold input bytes
+    const int lane = threadIdx.x & 31;
+    for (;;) {
+        uint32_t first = 0u;
+        if (lane == 0) first = atomicAdd(ticket, 32u);
+        first = __shfl_sync(0xFFFFFFFFu, first, 0);
+        if ((uint64_t)first >= n_chunks) break;
+        const uint64_t g = (uint64_t)first + lane;
+        if (g >= n_chunks) continue;
+        uint64_t lo, hi;
+        chunk_span(g, cs, n, doc_off, chunk_base, n_docs, &lo, &hi);
+        const uint32_t len = (uint32_t)(hi - lo);
+        const uint64_t w_first = (lo + shift) >> 2;                     // word holding the chunk's first byte
+        const uint32_t* __restrict__ cw = words + w_first;
+        const uint32_t a0 = (uint32_t)((lo + shift) & 3u);              // and that byte's place in it
+        const uint32_t w_avail = (uint32_t)min((unsigned long long)(last_word - w_first), 0xFFFFFFFFull);
+        uint32_t* __restrict__ out = staging + g * cs;
+        // a window of two words: the bytes at q and q + 1 come out of one funnel shift
+        uint32_t widx = 0u;
+        uint32_t word0 = __ldg(cw), word1 = 1u < w_avail ? __ldg(cw + 1) : 0u;
+        uint32_t tw = 0;
+        uint32_t p = 0, w = 0, l = 0;   // token start, walk position, end of the longest token so far
+        uint32_t v = 0u, last = 0u, fb = 0u;
+        bool have = false;
+        while (p < len) {
+            const uint32_t qq = a0 + w;
+            if ((qq >> 2) != widx) {   // the walk position moves by at most two bytes per iteration and never back past p
+                const uint32_t nw = qq >> 2;
+                if (nw == widx + 1u) { word0 = word1; }
+                else { word0 = __ldg(cw + nw); }
+                widx = nw;
+                word1 = widx + 1u < w_avail ? __ldg(cw + widx + 1u) : 0u;
+                if ((widx & 7u) == 0u && widx + 24u < w_avail) asm volatile("prefetch.global.L1 [%0];" ::"l"(cw + widx + 16));
+            }
+            const uint32_t two_bytes = __funnelshift_r(word0, word1, (qq & 3u) * 8u);
+            const uint32_t b = two_bytes & 0xFFu, b2 = (two_bytes >> 8) & 0xFFu;
+            const bool fresh = w == p;
+            const bool two = fresh && (w + 1u < len);
+            const uint32_t n1 = t1[b];                      // the root's child for this byte (T_MISS: none)
+            fb = fresh ? b : fb;
+            const uint32_t key = fresh ? (((HY_ROOT2 | b) << 8) | b2) : (((v & HY_INDEX) << 8) | b);
+            const uint32_t h0 = (key * mul0) & HY_KEY_MASK, h1 = (key * mul1) & HY_KEY_MASK;
+            const uint2 e0 = hot0[h0 >> HY_REM_SHIFT], e1 = hot1[h1 >> HY_REM_SHIFT];
+            const uint32_t r0 = h0 & ((1u << HY_REM_SHIFT) - 1u), r1 = h1 & ((1u << HY_REM_SHIFT) - 1u);
+            uint32_t nv = T_MISS;
+            nv = (e0.x >> 19) == r0 ? e0.x : nv;
+            nv = (e0.y >> 19) == r0 ? e0.y : nv;
+            nv = (e1.x >> 19) == r1 ? e1.x : nv;
+            nv = (e1.y >> 19) == r1 ? e1.y : nv;
+            bool hit = (nv & HY_INDEX) != HY_INDEX && (two || !fresh);   // an empty entry is all ones
+            if (!hit && !fresh) {
+                // some of this node's children may live in the global table only
+                const uint32_t vi = v & HY_INDEX;
+                if ((__ldg(t.cold_bits + (vi >> 5)) >> (vi & 31u)) & 1u) {
+                    const uint32_t hh = key * 0x9E3779B1u;
+                    uint32_t slot = (hh ^ (hh >> 15)) & t.cold_mask;
+                    for (;;) {
+                        const uint2 e = __ldg(t.cold + slot);
+                        if (e.x == key) { nv = e.y; hit = true; break; }
+                        if (e.x == T_EMPTY_KEY) break;
+                        slot = (slot + 1) & t.cold_mask;
+                    }
+                }
+            }
+            if (fresh) {   // what the first byte alone is worth
+                have = n1 != T_MISS && (n1 & HY_HAS_TOKEN) != 0u;
+                last = n1 & HY_INDEX;
+                l = p + 1u;
+            }
+            if (hit) {
+                v = nv;
+                w = fresh ? p + 2u : w + 1u;
+                if (nv & HY_HAS_TOKEN) { have = true; last = nv & HY_INDEX; l = w; }
+            }
+            const bool ends = !hit || (nv & HY_LEAF) != 0u || w >= len;
+            if (ends) {
+                out[tw++] = have ? last : fb;
+                p = have ? l : p + 1u;
+                w = p;
+            }
         }
         counts[g] = tw;
     }
@@ -397,6 +533,14 @@ struct Tokenizer {
     int ck_d = 0;                  // its number of sub-tables (0: the global table is in use)
     uint32_t ck_log2 = 0, ck_mul[3] = {1u, 1u, 1u};
     uint32_t root = T_ROOT;
+    // medium tries: the hybrid layout
+    bool hybrid = false;
+    uint32_t* d_hot = nullptr;       // shared-memory image: the bucketed cuckoo table, then the root's 256 children
+    uint2* d_cold = nullptr;
+    uint32_t* d_cold_bits = nullptr;
+    uint32_t hy_mul[2] = {1u, 1u}, cold_mask = 0, hot_entries = 0;
+    uint64_t batch_slice_bytes = 32ull << 20;   // host batches above twice this are encoded slice by slice
+    uint64_t encode_slice_bytes = 8ull << 30;   // b200bpe_encode: larger inputs go through in chunk-aligned slices
     // pooled work buffers (grown on demand, as tokenizer.js:108-166 does)
     uint8_t* d_in = nullptr; uint64_t in_cap = 0;
     uint32_t* d_staging = nullptr; uint64_t staging_cap = 0;   // elements
@@ -415,7 +559,7 @@ struct Tokenizer {
 
     ~Tokenizer() {
         if (ctx) cudaSetDevice(ctx->device);
-        cudaFree(d_trans); cudaFree(d_cuckoo); cudaFree(d_in); cudaFree(d_staging);
+        cudaFree(d_trans); cudaFree(d_cuckoo); cudaFree(d_hot); cudaFree(d_cold); cudaFree(d_cold_bits); cudaFree(d_in); cudaFree(d_staging);
         cudaFree(d_counts); cudaFree(d_chunk_off); cudaFree(d_out); cudaFree(d_doc_off); cudaFree(d_chunk_base);
         cudaFree(d_tok_off); cudaFree(d_desc); cudaFree(d_ctl); cudaFree(d_total);
         if (h_total) cudaFreeHost(h_total);
@@ -451,7 +595,7 @@ struct Tokenizer {
         return B200BPE_OK;
     }
 
-    size_t walk_smem() const { return ck_d == 0 ? (size_t)TW_SMEM_BYTES : ((size_t)ck_d << ck_log2) * 4; }
+    size_t walk_smem() const { return hybrid ? (size_t)HY_SMEM_BYTES : ck_d == 0 ? (size_t)TW_SMEM_BYTES : ((size_t)ck_d << ck_log2) * 4; }
 
     // The walk kernel for this tokenizer's trie layout; max_chunks only sizes the grid.
     void walk(const uint8_t* d_bytes, uint64_t n, const uint64_t* d_docs, const uint64_t* cb, uint32_t n_docs,
@@ -459,7 +603,11 @@ struct Tokenizer {
         cudaStream_t s = ctx->stream;
         TrieDev t{d_trans, trans_mask, d_cuckoo, ck_log2, {ck_mul[0], ck_mul[1], ck_mul[2]}, root};
         const uint64_t n_static = (n + chunk - 1) / chunk;
-        if (ck_d == 0) {
+        if (hybrid) {
+            TrieHybrid th{d_hot, {hy_mul[0], hy_mul[1]}, d_cold, cold_mask, d_cold_bits};
+            const int grid = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)ctx->sm_count * HY_CTAS, (max_chunks + HY_THREADS - 1) / HY_THREADS));
+            k_trie_walk_hybrid<<<grid, HY_THREADS, HY_SMEM_BYTES, s>>>(th, d_bytes, n, chunk, d_docs, cb, n_docs, n_static, staging, counts, ticket);
+        } else if (ck_d == 0) {
             const int grid = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)ctx->sm_count * 3, (max_chunks + TW_THREADS - 1) / TW_THREADS));
             k_trie_walk<TW_THREADS, TW_CACHE_LOG2, 0><<<grid, TW_THREADS, walk_smem(), s>>>(
                 t, d_bytes, n, chunk, d_docs, cb, n_docs, n_static, staging, counts, ticket);
@@ -483,7 +631,7 @@ struct Tokenizer {
         cudaStream_t s = ctx->stream;
         uint64_t* hd = h_dst ? h_dst : h_total;
         cudaEvent_t* ev = evs ? evs : this->ev;
-        if (ck_d == 0) set_persisting_window(ctx, d_trans, trans_bytes);  // keep the transition table resident in L2
+        if (ck_d == 0 && !hybrid) set_persisting_window(ctx, d_trans, trans_bytes);  // keep the transition table resident in L2
         const uint64_t max_chunks = (n + chunk - 1) / chunk + (d_docs ? n_docs : 0);
         b200bpe_status r = ensure_work(std::max<uint64_t>(1, max_chunks));
         if (r) return r;
@@ -553,7 +701,18 @@ extern "C" {
 
 b200bpe_status b200bpe_tokenizer_create(b200bpe_ctx* c, const void* trie, size_t len, uint32_t chunk_size,
                                         b200bpe_tok** out) {
-    if (!c || !trie || !out) return B200BPE_ERR_BAD_ARG;
+    b200bpe_tok_opts o;
+    std::memset(&o, 0, sizeof(o));
+    o.struct_size = sizeof(o);
+    o.chunk_size = chunk_size;
+    return b200bpe_tokenizer_create_ex(c, trie, len, &o, out);
+}
+
+b200bpe_status b200bpe_tokenizer_create_ex(b200bpe_ctx* c, const void* trie, size_t len, const b200bpe_tok_opts* opts,
+                                           b200bpe_tok** out) {
+    if (!c || !trie || !out || !opts || opts->struct_size != sizeof(b200bpe_tok_opts)) return B200BPE_ERR_BAD_ARG;
+    if (opts->layout > B200BPE_TRIE_HASH) return B200BPE_ERR_BAD_ARG;
+    const uint32_t chunk_size = opts->chunk_size;
     uint32_t f[5];
     b200bpe_status r = b200bpe_trie_parse_header(trie, len, f);
     if (r) return r;
@@ -637,8 +796,7 @@ b200bpe_status b200bpe_tokenizer_create(b200bpe_ctx* c, const void* trie, size_t
     std::vector<uint32_t> cuckoo;
     int ck_d = 0;
     uint32_t ck_log2 = 0, ck_mul[3] = {1u, 1u, 1u};
-    const char* layout = std::getenv("B200BPE_TRIE_LAYOUT");
-    const bool want_cuckoo = !(layout && std::strcmp(layout, "hash") == 0);
+    const bool want_cuckoo = opts->layout == B200BPE_TRIE_AUTO || opts->layout == B200BPE_TRIE_CUCKOO;
     if (want_cuckoo && root_index <= CK_INDEX) {
         uint64_t rng = 0x9E3779B97F4A7C15ull ^ ((uint64_t)edges.size() << 20);
         auto next_rand = [&]() { rng ^= rng << 13; rng ^= rng >> 7; rng ^= rng << 17; return rng; };
@@ -690,10 +848,152 @@ b200bpe_status b200bpe_tokenizer_create(b200bpe_ctx* c, const void* trie, size_t
             }
         }
     }
+    // Medium tries: the hybrid layout (see the head of this file).
+    std::vector<uint32_t> hot;        // the shared-memory image
+    std::vector<uint2> cold;
+    std::vector<uint32_t> cold_bits;
+    uint32_t hy_mul[2] = {1u, 1u}, cold_mask = 0, hot_entries = 0;
+    bool hybrid = false;
+    const bool want_hybrid = opts->layout == B200BPE_TRIE_HYBRID || (opts->layout == B200BPE_TRIE_AUTO && ck_d == 0);
+    if (want_hybrid && ck_d == 0 && root_index < HY_MAX_INDEX) {
+        auto pack = [&](uint32_t node) {
+            return dev_index[node] | (is_token(node) ? HY_HAS_TOKEN : 0u) | (is_leaf(node) ? HY_LEAF : 0u);
+        };
+        // children of a node: first of equal symbols only, as above
+        auto for_children = [&](uint32_t node, auto&& fn) {
+            const uint32_t fc = nodes[(size_t)node * 3], nc = nodes[(size_t)node * 3 + 1] & 0xFFFFu;
+            uint32_t seen_sym[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (uint32_t e = fc; e < fc + nc; e++) {
+                const uint32_t sy = esym[e] & 0xFFu;
+                if ((seen_sym[sy >> 5] >> (sy & 31u)) & 1u) continue;
+                seen_sym[sy >> 5] |= 1u << (sy & 31u);
+                fn(sy, etgt[e]);
+            }
+        };
+        // depth of every node and the smallest token id at or below it (iterative, cycle-safe: a node is visited once)
+        std::vector<uint32_t> depth(node_count, 0xFFFFFFFFu), best(node_count, 0xFFFFFFFFu), order;
+        order.reserve(node_count);
+        depth[0] = 0;
+        order.push_back(0);
+        for (size_t i = 0; i < order.size(); i++)
+            for_children(order[i], [&](uint32_t, uint32_t ch) {
+                if (depth[ch] == 0xFFFFFFFFu) { depth[ch] = depth[order[i]] + 1; order.push_back(ch); }
+            });
+        for (size_t i = order.size(); i-- > 0;) {
+            const uint32_t nd = order[i];
+            if (is_token(nd)) best[nd] = std::min(best[nd], nodes[(size_t)nd * 3 + 2]);
+            for_children(nd, [&](uint32_t, uint32_t ch) { best[nd] = std::min(best[nd], best[ch]); });
+        }
+        struct Cand { uint32_t key, value, rank, parent; };
+        std::vector<Cand> root2, deep;
+        std::vector<uint32_t> t1(256, T_MISS);
+        for_children(0, [&](uint32_t b0, uint32_t c1) {
+            t1[b0] = pack(c1);
+            for_children(c1, [&](uint32_t b1, uint32_t c2) { root2.push_back({((HY_ROOT2 | b0) << 8) | b1, pack(c2), 0u, 0u}); });
+        });
+        for (uint32_t nd : order)
+            if (depth[nd] >= 2)
+                for_children(nd, [&](uint32_t b, uint32_t ch) { deep.push_back({(dev_index[nd] << 8) | b, pack(ch), best[ch], dev_index[nd]}); });
+        // Whole parents go into shared memory, most used first (rank of a parent: the smallest token id at or
+        // below it): a miss under a parent that is there completely needs no look at the global table, and
+        // nearly every token ends with such a miss.
+        for (Cand& d : deep) d.rank = 0u;
+        {
+            std::vector<uint32_t> rank_of(root_index + 1, 0xFFFFFFFFu);
+            for (uint32_t nd : order) if (depth[nd] >= 2) rank_of[dev_index[nd]] = best[nd];
+            for (Cand& d : deep) d.rank = rank_of[d.parent];
+        }
+        std::stable_sort(deep.begin(), deep.end(), [](const Cand& a, const Cand& b) { return a.rank != b.rank ? a.rank < b.rank : a.parent < b.parent; });
+        const uint32_t buckets = 1u << HY_BUCKET_LOG2, rem_mask = (1u << HY_REM_SHIFT) - 1u;
+        const size_t hot_cap = (size_t)(HY_MAX_LOAD * (double)HY_HOT_WORDS);
+        uint64_t rng = 0xD1B54A32D192ED03ull ^ ((uint64_t)deep.size() << 17);
+        auto next_rand = [&]() { rng ^= rng << 13; rng ^= rng >> 7; rng ^= rng << 17; return rng; };
+        for (int attempt = 0; attempt < 64 && !hybrid && root2.size() * 2 <= hot_cap; attempt++) {
+            uint32_t mul[2];
+            for (int j = 0; j < 2; j++) mul[j] = ((uint32_t)(next_rand() >> 20) | 1u) & HY_KEY_MASK;
+            std::vector<uint32_t> tab(HY_HOT_WORDS, 0xFFFFFFFFu);
+            std::vector<Cand> owner(HY_HOT_WORDS);
+            // A key is never placed where a look-up could take an empty entry (remainder all ones) for it.
+            auto usable = [&](uint32_t key) {
+                for (int j = 0; j < 2; j++) if ((((key * mul[j]) & HY_KEY_MASK) & rem_mask) == rem_mask) return false;
+                return true;
+            };
+            // random-walk insertion; every write is logged so that a failed insertion can be undone
+            struct Undo { size_t slot; uint32_t word; Cand who; };
+            std::vector<Undo> undo;
+            auto insert = [&](Cand cur) -> bool {
+                undo.clear();
+                for (int kick = 0; kick < 500; kick++) {
+                    size_t free_slot = SIZE_MAX;
+                    uint32_t hj[2];
+                    for (int j = 0; j < 2; j++) {
+                        hj[j] = (cur.key * mul[j]) & HY_KEY_MASK;
+                        const size_t base = ((size_t)j * buckets + (hj[j] >> HY_REM_SHIFT)) * 2;
+                        for (int e = 0; e < 2 && free_slot == SIZE_MAX; e++) if (tab[base + e] == 0xFFFFFFFFu) free_slot = base + e;
+                    }
+                    if (free_slot != SIZE_MAX) {
+                        const int j = (int)(free_slot / ((size_t)buckets * 2));
+                        undo.push_back({free_slot, tab[free_slot], owner[free_slot]});
+                        tab[free_slot] = ((hj[j] & rem_mask) << 19) | cur.value;
+                        owner[free_slot] = cur;
+                        return true;
+                    }
+                    const int j = (int)(next_rand() & 1u);
+                    const size_t slot = ((size_t)j * buckets + (hj[j] >> HY_REM_SHIFT)) * 2 + (size_t)(next_rand() & 1u);
+                    const Cand evicted = owner[slot];
+                    undo.push_back({slot, tab[slot], evicted});
+                    tab[slot] = ((hj[j] & rem_mask) << 19) | cur.value;
+                    owner[slot] = cur;
+                    cur = evicted;
+                }
+                for (size_t i = undo.size(); i-- > 0;) { tab[undo[i].slot] = undo[i].word; owner[undo[i].slot] = undo[i].who; }
+                return false;
+            };
+            bool ok = true;
+            size_t placed = 0;
+            for (const Cand& r : root2) { if (!usable(r.key) || !insert(r)) { ok = false; break; } placed++; }
+            if (!ok) continue;
+            // the deeper transitions, most used first, while there is room
+            std::vector<uint8_t> in_hot(deep.size(), 0);
+            for (size_t i = 0; i < deep.size();) {
+                size_t j = i;
+                while (j < deep.size() && deep[j].parent == deep[i].parent) j++;   // the children of one parent
+                if (placed + (j - i) <= hot_cap) {
+                    for (size_t k = i; k < j; k++) {
+                        if (!usable(deep[k].key) || !insert(deep[k])) break;   // a failed insertion is undone; the parent then counts as cold
+                        in_hot[k] = 1;
+                        placed++;
+                    }
+                }
+                i = j;
+            }
+            hot.assign(tab.begin(), tab.end());
+            hot.insert(hot.end(), t1.begin(), t1.end());
+            hot_entries = (uint32_t)placed;
+            // the rest go to the global table, and their parents are marked
+            size_t n_cold = 0;
+            for (size_t i = 0; i < deep.size(); i++) n_cold += in_hot[i] ? 0 : 1;
+            uint32_t clog = 4;
+            while ((1ull << clog) < (uint64_t)n_cold * 2 + 16) clog++;
+            cold.assign((size_t)1 << clog, make_uint2(T_EMPTY_KEY, 0u));
+            cold_mask = (1u << clog) - 1;
+            cold_bits.assign((root_index >> 5) + 2, 0u);
+            for (size_t i = 0; i < deep.size(); i++) {
+                if (in_hot[i]) continue;
+                const uint32_t hh = deep[i].key * 0x9E3779B1u;
+                uint32_t slot = (hh ^ (hh >> 15)) & cold_mask;
+                while (cold[slot].x != T_EMPTY_KEY) slot = (slot + 1) & cold_mask;
+                cold[slot] = make_uint2(deep[i].key, deep[i].value);
+                cold_bits[deep[i].parent >> 5] |= 1u << (deep[i].parent & 31u);
+            }
+            hy_mul[0] = mul[0]; hy_mul[1] = mul[1];
+            hybrid = true;
+        }
+    }
     // Larger tries (or on request): open addressing in global memory.
     std::vector<uint2> trans;
     uint32_t tmask = 0;
-    if (ck_d == 0) {
+    if (ck_d == 0 && !hybrid) {
         uint32_t tlog = 4;
         while ((1ull << tlog) < (uint64_t)edges.size() * 2 + 16) tlog++;
         trans.assign((size_t)1 << tlog, make_uint2(T_EMPTY_KEY, 0u));
@@ -717,10 +1017,24 @@ b200bpe_status b200bpe_tokenizer_create(b200bpe_ctx* c, const void* trie, size_t
     t->root = root_index;
     t->ck_d = ck_d; t->ck_log2 = ck_log2;
     for (int j = 0; j < 3; j++) t->ck_mul[j] = ck_mul[j];
+    t->hybrid = hybrid;
+    t->hy_mul[0] = hy_mul[0]; t->hy_mul[1] = hy_mul[1];
+    t->cold_mask = cold_mask;
+    t->hot_entries = hot_entries;
+    if (opts->batch_slice_bytes >= 1024) t->batch_slice_bytes = opts->batch_slice_bytes;
+    if (opts->encode_slice_bytes >= 1024) t->encode_slice_bytes = opts->encode_slice_bytes;
     cudaStream_t s = c->c.stream;
     auto fail = [&](b200bpe_status st) { delete t; return st; };
 #define B2_TRY(expr) if ((expr) != cudaSuccess) { set_last_error(std::string(#expr) + ": " + cudaGetErrorString(cudaGetLastError())); return fail(B200BPE_ERR_CUDA); }
-    if (ck_d == 0) {
+    if (hybrid) {
+        B2_TRY(cudaMalloc(&t->d_hot, hot.size() * 4));
+        B2_TRY(cudaMemcpyAsync(t->d_hot, hot.data(), hot.size() * 4, cudaMemcpyHostToDevice, s));
+        B2_TRY(cudaMalloc(&t->d_cold, cold.size() * 8));
+        B2_TRY(cudaMemcpyAsync(t->d_cold, cold.data(), cold.size() * 8, cudaMemcpyHostToDevice, s));
+        B2_TRY(cudaMalloc(&t->d_cold_bits, cold_bits.size() * 4));
+        B2_TRY(cudaMemcpyAsync(t->d_cold_bits, cold_bits.data(), cold_bits.size() * 4, cudaMemcpyHostToDevice, s));
+        B2_TRY(cudaFuncSetAttribute(k_trie_walk_hybrid, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)HY_SMEM_BYTES));
+    } else if (ck_d == 0) {
         B2_TRY(cudaMalloc(&t->d_trans, trans.size() * 8));
         B2_TRY(cudaMemcpyAsync(t->d_trans, trans.data(), trans.size() * 8, cudaMemcpyHostToDevice, s));
         B2_TRY(cudaFuncSetAttribute(k_trie_walk<TW_THREADS, TW_CACHE_LOG2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -760,10 +1074,11 @@ b200bpe_status b200bpe_tokenizer_info(b200bpe_tok* h, uint32_t* node_count, uint
 b200bpe_status b200bpe_tokenizer_layout(b200bpe_tok* h, uint32_t* sub_tables, uint32_t* log2_slots) {
     if (!h) return B200BPE_ERR_BAD_ARG;
     const Tokenizer* t = h->t;
-    if (sub_tables) *sub_tables = (uint32_t)t->ck_d;
+    if (sub_tables) *sub_tables = t->hybrid ? 1u : (uint32_t)t->ck_d;
     if (log2_slots) {
         uint32_t k = t->ck_log2;
-        if (t->ck_d == 0) for (k = 0; (1u << k) <= t->trans_mask; k++) {}
+        if (t->hybrid) k = HY_BUCKET_LOG2 + 2;
+        else if (t->ck_d == 0) for (k = 0; (1u << k) <= t->trans_mask; k++) {}
         *log2_slots = k;
     }
     return B200BPE_OK;
@@ -803,7 +1118,7 @@ b200bpe_status b200bpe_encode(b200bpe_tok* h, const uint8_t* bytes, uint64_t n, 
     cudaStream_t s = t->ctx->stream;
     // Inputs beyond 8 GiB go through in chunk-aligned slices, as tokenizer.js:181-203 slices to its
     // buffer limit; the result is the same as one pass because slices end on chunk boundaries.
-    const uint64_t slice = ((8ull << 30) / t->chunk) * t->chunk;
+    const uint64_t slice = std::max<uint64_t>(1, t->encode_slice_bytes / t->chunk) * t->chunk;
     uint64_t done_tokens = 0;
     for (uint64_t off = 0; off < n; off += slice) {
         const uint64_t m = std::min(slice, n - off);
@@ -823,8 +1138,6 @@ b200bpe_status b200bpe_encode(b200bpe_tok* h, const uint8_t* bytes, uint64_t n, 
     return B200BPE_OK;
 }
 
-constexpr uint64_t BATCH_SLICE_BYTES = 32ull << 20;   // host batches above twice this are encoded slice by slice
-
 b200bpe_status b200bpe_encode_batch(b200bpe_tok* h, const uint8_t* bytes, const uint64_t* doc_offsets, uint32_t n_docs,
                                     uint32_t* tokens_out, uint64_t cap, uint64_t* tok_offsets_out) {
     if (!h || !doc_offsets || !tok_offsets_out) return B200BPE_ERR_BAD_ARG;
@@ -837,11 +1150,7 @@ b200bpe_status b200bpe_encode_batch(b200bpe_tok* h, const uint8_t* bytes, const 
     // run while the tokens of the slices before it travel back (documents are independent, so the
     // result does not depend on the cut).
     std::vector<uint32_t> cut{0};
-    uint64_t slice_bytes = BATCH_SLICE_BYTES;
-    if (const char* e = std::getenv("B200BPE_BATCH_SLICE_BYTES")) {   // tests use small slices
-        const unsigned long long v = std::strtoull(e, nullptr, 10);
-        if (v >= 1024) slice_bytes = v;
-    }
+    const uint64_t slice_bytes = t->batch_slice_bytes;
     if (n > 2 * slice_bytes) {
         uint64_t start = doc_offsets[0];
         for (uint32_t d = 1; d < n_docs; d++)

@@ -25,8 +25,15 @@ class TrieTokenizer:
         header = parseHeader(trieData)   # raises the reference's errors for bad magic / version / length
         buf = np.frombuffer(trieData, np.uint8)
         h = C.c_void_p()
-        st = _lib.lib().b200bpe_tokenizer_create(engine.ctx, buf.ctypes.data, buf.size, int(options.get("chunkSize") or 0),
-                                                 C.byref(h))
+        # chunkSize is the reference's option (tokenizer.js:67-68); layout / batchSliceBytes / encodeSliceBytes are this
+        # library's (results never depend on them)
+        o = _lib.TokOpts()
+        o.struct_size = C.sizeof(_lib.TokOpts)
+        o.chunk_size = int(options.get("chunkSize") or 0)
+        o.layout = _lib.TRIE_LAYOUTS[options.get("layout") or "auto"]
+        o.batch_slice_bytes = int(options.get("batchSliceBytes") or 0)
+        o.encode_slice_bytes = int(options.get("encodeSliceBytes") or 0)
+        st = _lib.lib().b200bpe_tokenizer_create_ex(engine.ctx, buf.ctypes.data, buf.size, C.byref(o), C.byref(h))
         if st == 9:
             raise ValueError("Truncated trie data")
         _lib.check(st, "b200bpe_tokenizer_create")
@@ -37,7 +44,7 @@ class TrieTokenizer:
         self.chunkSize = cs.value
         d, k = C.c_uint32(), C.c_uint32()
         _lib.lib().b200bpe_tokenizer_layout(h, C.byref(d), C.byref(k))
-        self.deviceLayout = (d.value, k.value)   # (cuckoo sub-tables or 0, log2 of the slots per table)
+        self.deviceLayout = (d.value, k.value)   # (2 / 3 cuckoo sub-tables, 1 hybrid, 0 global hash; log2 of the slots)
 
     @staticmethod
     def fromVocab(engine, vocab, options: dict | None = None) -> "TrieTokenizer":

@@ -177,10 +177,28 @@ b200bpe_status b200bpe_trie_parse_header(const void* trie, size_t len, uint32_t 
  * chunk_size 0 selects the reference rule max(512, min(2048, maxTokenLen*8)) (tokenizer.js:67-68). */
 b200bpe_status b200bpe_tokenizer_create(b200bpe_ctx*, const void* trie_v3, size_t len, uint32_t chunk_size,
                                         b200bpe_tok** out);
+/* The same with every option spelled out (zero-initialise, set struct_size; 0 = default everywhere).
+ * layout picks how the trie lies on the device; the slice sizes are the points at which
+ * b200bpe_encode_batch (default 32 MiB of documents) and b200bpe_encode (default 8 GiB, the analogue
+ * of the buffer limit of tokenizer.js:181-203) cut their input.  Results never depend on any of them;
+ * tests use them to reach every code path with small inputs. */
+enum { B200BPE_TRIE_AUTO = 0, B200BPE_TRIE_CUCKOO = 1, B200BPE_TRIE_HYBRID = 2, B200BPE_TRIE_HASH = 3 };
+typedef struct {
+    uint32_t struct_size;        /* sizeof(b200bpe_tok_opts) */
+    uint32_t chunk_size;         /* tokenizer.js:67-68 options.chunkSize; 0 = the reference rule */
+    uint32_t layout;             /* B200BPE_TRIE_*; a layout the trie does not fit falls through to the next one */
+    uint32_t reserved;
+    uint64_t batch_slice_bytes;  /* 0 = default; at least 1024 */
+    uint64_t encode_slice_bytes; /* 0 = default; at least 1024 (rounded down to whole chunks) */
+} b200bpe_tok_opts;
+b200bpe_status b200bpe_tokenizer_create_ex(b200bpe_ctx*, const void* trie_v3, size_t len, const b200bpe_tok_opts*,
+                                           b200bpe_tok** out);
 b200bpe_status b200bpe_tokenizer_info(b200bpe_tok*, uint32_t* node_count, uint32_t* edge_count,
                                       uint32_t* max_token_len, uint32_t* chunk_size);
 /* How the trie lies on the device (no reference counterpart; for diagnostics and tests):
  * sub_tables 2 or 3 = cuckoo table held in shared memory, with 1 << log2_slots entries each;
+ * sub_tables 1 = hybrid: the most used transitions (1 << log2_slots entries, two-byte first step) in shared
+ *                memory, the rest in a global table;
  * sub_tables 0 = open-addressing table in global memory with 1 << log2_slots entries. */
 b200bpe_status b200bpe_tokenizer_layout(b200bpe_tok*, uint32_t* sub_tables, uint32_t* log2_slots);
 /* encodeBytes (tokenizer.js:173-206): host bytes in, host token ids out.  cap is the room in

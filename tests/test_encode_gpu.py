@@ -10,13 +10,17 @@ from tests.helpers import small_text
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=["auto", "hash"])
+@pytest.fixture(autouse=True, params=["auto", "hybrid", "hash"])
 def trie_layout(request, monkeypatch):
-    """Every test runs on both device layouts of the trie: the one the library picks, and the global hash table forced."""
-    if request.param == "hash":
-        monkeypatch.setenv("B200BPE_TRIE_LAYOUT", "hash")
-    else:
-        monkeypatch.delenv("B200BPE_TRIE_LAYOUT", raising=False)
+    """Every test runs on three device layouts of the trie: the one the library picks (for these vocabularies the
+    cuckoo table in shared memory), the hybrid (hot transitions in shared memory, two-byte first step) and the global
+    hash table.  The layout is an option of the tokenizer; it is set here for every tokenizer a test makes."""
+    real_init = TrieTokenizer.__init__
+
+    def init(self, engine, trieData, vocab=None, options=None):
+        real_init(self, engine, trieData, vocab, dict(options or {}, layout=request.param))
+
+    monkeypatch.setattr(TrieTokenizer, "__init__", init)
     return request.param
 
 
@@ -32,7 +36,7 @@ def trained():
 def test_tokenizer_fields_and_chunk_rule(engine, trained, trie_layout):
     vocab, trie = trained
     tok = TrieTokenizer.fromVocab(engine, vocab)
-    assert (tok.deviceLayout[0] == 0) == (trie_layout == "hash")
+    assert tok.deviceLayout[0] == {"auto": 2, "hybrid": 1, "hash": 0}[trie_layout] or (trie_layout == "auto" and tok.deviceLayout[0] == 3)
     hdr = M.parse_trie(trie)
     assert (tok.nodeCount, tok.edgeCount, tok.maxTokenLen) == (hdr["nodeCount"], hdr["edgeCount"], hdr["maxTokenLen"])
     assert tok.chunkSize == max(512, min(2048, hdr["maxTokenLen"] * 8))
@@ -131,9 +135,10 @@ def test_train_then_encode_round_trip(engine):
     tok.destroy()
 
 
-@pytest.mark.parametrize("n_tokens,alphabet,want_tables", [(3_000, 64, 2), (14_000, 24, 3), (70_000, 256, 0)])
+@pytest.mark.parametrize("n_tokens,alphabet,want_tables", [(3_000, 64, 2), (14_000, 24, 3), (70_000, 64, 1), (140_000, 256, 0)])
 def test_trie_sizes_pick_their_layout(engine, trie_layout, n_tokens, alphabet, want_tables):
-    """Random vocabularies sized for two cuckoo sub-tables, for three, and too large for shared memory."""
+    """Random vocabularies sized for two cuckoo sub-tables, for three, for the hybrid (too large for shared
+    memory, every node index below 130,816) and for the global table alone."""
     rng = np.random.default_rng(n_tokens)
     vocab = [[b] for b in range(256)]
     seen = set()
@@ -144,14 +149,15 @@ def test_trie_sizes_pick_their_layout(engine, trie_layout, n_tokens, alphabet, w
             vocab.append(list(t))
     trie = M.compile_vocab_to_trie(vocab)
     tok = TrieTokenizer(engine, trie, vocab)
-    assert tok.deviceLayout[0] == (0 if trie_layout == "hash" else want_tables), tok.deviceLayout
+    want = {"auto": want_tables, "hash": 0, "hybrid": 1 if want_tables else 0}[trie_layout]   # a trie too large for the hybrid falls through
+    assert tok.deviceLayout[0] == want, tok.deviceLayout
     data = rng.integers(0, alphabet, 400_000, dtype=np.uint8)
     data[::97] = 255  # and bytes outside the alphabet
     assert tok.encodeBytes(data).tolist() == O.encode(data, trie, tok.chunkSize, threads=4).tolist()
     tok.destroy()
 
 
-def test_batch_in_slices_equals_one_pass(engine, trained, monkeypatch):
+def test_batch_in_slices_equals_one_pass(engine, trained):
     """Large host batches are encoded slice by slice with the read-back of one slice under the work of
     the next; the cut must not show (here forced with small slices)."""
     from gpu_bpe_b200 import synth
@@ -160,12 +166,27 @@ def test_batch_in_slices_equals_one_pass(engine, trained, monkeypatch):
     offs = synth.doc_offsets(9, data.size, 257, 1.2)
     offs[17] = offs[16]          # an empty document
     tok = TrieTokenizer(engine, trie, vocab)
-    monkeypatch.delenv("B200BPE_BATCH_SLICE_BYTES", raising=False)
     toks1, toff1 = tok.encodeBatch(data, offs)
     for slice_bytes in (4096, 65536, 300_000):
-        monkeypatch.setenv("B200BPE_BATCH_SLICE_BYTES", str(slice_bytes))
-        toks2, toff2 = tok.encodeBatch(data, offs)
+        sliced = TrieTokenizer(engine, trie, vocab, {"batchSliceBytes": slice_bytes})
+        toks2, toff2 = sliced.encodeBatch(data, offs)
+        sliced.destroy()
         assert np.array_equal(toks1, toks2) and np.array_equal(toff1, toff2), slice_bytes
     assert toks1.tolist() == np.concatenate([O.encode(data[int(offs[d]):int(offs[d + 1])], trie, tok.chunkSize)
                                              if offs[d + 1] > offs[d] else np.zeros(0, np.uint32) for d in range(257)]).tolist()
+    tok.destroy()
+
+
+def test_encode_in_slices_equals_one_pass(engine, trained):
+    """encodeBytes cuts inputs beyond its buffer limit into chunk-aligned slices (tokenizer.js:181-203); with the
+    limit forced down to 100,000 bytes a 300,001-byte input goes through in four slices and the cut must not show."""
+    vocab, trie = trained
+    data, _, _ = small_text(2, 82, 300_001)
+    tok = TrieTokenizer(engine, trie, vocab)
+    want = tok.encodeBytes(data)
+    assert want.tolist() == O.encode(data, trie, tok.chunkSize, threads=4).tolist()
+    for limit in (100_000, 512, 70_000):
+        sliced = TrieTokenizer(engine, trie, vocab, {"encodeSliceBytes": limit})
+        assert np.array_equal(sliced.encodeBytes(data), want), limit
+        sliced.destroy()
     tok.destroy()

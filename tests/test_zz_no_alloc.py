@@ -32,9 +32,10 @@ def _encode_both(tok, data: np.ndarray):
     return out_a[:na].cpu().numpy().astype(np.uint32), out_b[:nb].cpu().numpy().astype(np.uint32)
 
 
-def test_no_alloc_encode_matches_pooled_encode(engine):
+@pytest.mark.parametrize("layout", ["auto", "hybrid", "hash"])
+def test_no_alloc_encode_matches_pooled_encode(engine, layout):
     vocab = _vocab()
-    tok = TrieTokenizer.fromVocab(engine, vocab)
+    tok = TrieTokenizer.fromVocab(engine, vocab, {"layout": layout})
     trie = M.compile_vocab_to_trie(vocab)
     first, _, _ = small_text(2, 90, 1 << 20)          # the largest input the entry point takes
     second, _, _ = small_text(2, 91, 300_001)         # shorter: the array still holds the first call's data
