@@ -25,11 +25,12 @@ STATUS = {0: "OK", 1: "BAD_ARG", 2: "CUDA", 3: "NO_DEVICE", 4: "EMPTY_CORPUS", 5
 class TrainOpts(C.Structure):
     _fields_ = [("struct_size", C.c_uint32), ("target_vocab_size", C.c_uint32), ("first_token_id", C.c_uint32),
                 ("batch_merges", C.c_uint32), ("compat_mode", C.c_uint32), ("table_log2", C.c_uint32),
-                ("flags", C.c_uint32), ("exchange_cap", C.c_uint32)]
+                ("flags", C.c_uint32), ("exchange_cap", C.c_uint32), ("test_lookback_spins", C.c_uint32),
+                ("test_first_tile", C.c_uint32)]
 
 
 class TokOpts(C.Structure):
-    _fields_ = [("struct_size", C.c_uint32), ("chunk_size", C.c_uint32), ("layout", C.c_uint32), ("reserved", C.c_uint32),
+    _fields_ = [("struct_size", C.c_uint32), ("chunk_size", C.c_uint32), ("layout", C.c_uint32), ("test_lookback_spins", C.c_uint32),
                 ("batch_slice_bytes", C.c_uint64), ("encode_slice_bytes", C.c_uint64)]
 
 
@@ -99,6 +100,7 @@ SIGNATURES = {
     "b200bpe_tokenizer_destroy": (None, [C.c_void_p]),
     "b200bpe_pretokenize": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_void_p]),
     "b200bpe_pretokenize_device": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]),
+    "b200bpe_pretokenize_device_ex": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint32]),
     "b200bpe_pretokenize_gpu": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]),
     "b200bpe_dxft_size": (C.c_int32, [C.c_uint64, C.c_uint64, u64p]),
     "b200bpe_dxft_write": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_uint32, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64]),

@@ -81,7 +81,9 @@ struct DevState {
     uint32_t owned_log2;
     uint32_t owned_inserted; // keys inserted into the owned table since it was last emptied
     uint32_t xdone[2];      // CTAs of the route / accumulate kernels that have arrived at their end
-    uint32_t pad[4];        // the block is copied as 16-byte words
+    uint32_t lb_max_spins;  // polls after which a look-back of the merge kernel gives up (DS_LOOKBACK_TIMEOUT)
+    uint32_t first_ticket;  // first tile number the merge kernel hands out: 0, or 1 in the test of the bounded wait
+    uint32_t pad[2];        // the block is copied as 16-byte words
 };
 constexpr uint32_t CAND_CAP = 1u << 13;      // entries of the candidate list (one CTA scans it)
 constexpr uint32_t CAND_MAX_AGE = 512;       // merges after which a full scan is due anyway (refreshes the table's fill)

@@ -408,7 +408,7 @@ __global__ void __launch_bounds__(SC_THREADS)
 k_scan_compact(const uint32_t* __restrict__ staging, const uint32_t* __restrict__ counts, uint32_t cs,
                const uint64_t* __restrict__ chunk_base, uint32_t n_docs, uint64_t n_chunks_static,
                unsigned long long* __restrict__ desc, uint32_t* __restrict__ ctl, uint64_t* __restrict__ chunk_offsets,
-               uint32_t* __restrict__ out, uint64_t cap, uint64_t* __restrict__ total_out) {
+               uint32_t* __restrict__ out, uint64_t cap, uint64_t* __restrict__ total_out, uint32_t max_spins) {
     __shared__ uint64_t s_off[SC_THREADS];
     __shared__ uint32_t s_cnt[SC_THREADS];
     __shared__ uint32_t wsum[SC_THREADS / 32];
@@ -464,7 +464,7 @@ k_scan_compact(const uint32_t* __restrict__ staging, const uint32_t* __restrict_
                     for (;;) {
                         if (idx >= 0) d = ld_d64(desc + idx);
                         if (__all_sync(0xFFFFFFFFu, (d >> 62) != 0ull)) break;
-                        if (++spins > SC_MAX_SPINS) { timed_out = true; break; }
+                        if (++spins > max_spins) { timed_out = true; break; }
                         __nanosleep(40);
                     }
                     if (timed_out) break;
@@ -539,6 +539,8 @@ struct Tokenizer {
     uint2* d_cold = nullptr;
     uint32_t* d_cold_bits = nullptr;
     uint32_t hy_mul[2] = {1u, 1u}, cold_mask = 0, hot_entries = 0;
+    uint32_t sc_max_spins = SC_MAX_SPINS;       // polls after which the compaction's look-back gives up
+    bool skip_first_tile = false;               // test of that bounded wait: tile 0 is never worked on
     uint64_t batch_slice_bytes = 32ull << 20;   // host batches above twice this are encoded slice by slice
     uint64_t encode_slice_bytes = 8ull << 30;   // b200bpe_encode: larger inputs go through in chunk-aligned slices
     // pooled work buffers (grown on demand, as tokenizer.js:108-166 does)
@@ -638,6 +640,10 @@ struct Tokenizer {
         const uint64_t ntiles = max_chunks / SC_THREADS + 2;
         B2_CUDA(cudaMemsetAsync(d_desc, 0, ntiles * 8, s));
         B2_CUDA(cudaMemsetAsync(d_ctl, 0, 16, s));
+        if (skip_first_tile) {   // the tile ticket starts at 1
+            static const uint32_t one = 1u;
+            B2_CUDA(cudaMemcpyAsync(d_ctl, &one, 4, cudaMemcpyHostToDevice, s));
+        }
         const uint64_t* cb = nullptr;
         if (d_docs) {
             if ((r = ensure(&d_chunk_base, &chunk_base_cap, (uint64_t)n_docs + 1))) return r;
@@ -649,7 +655,7 @@ struct Tokenizer {
         B2_CUDA(cudaEventRecord(ev[1], s));
         const int grid_c = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)ctx->sm_count * 8, ntiles));
         k_scan_compact<<<grid_c, SC_THREADS, 0, s>>>(d_staging, d_counts, chunk, cb, n_docs, (n + chunk - 1) / chunk, d_desc,
-                                                    d_ctl, d_chunk_off, d_tokens, cap, d_total);
+                                                    d_ctl, d_chunk_off, d_tokens, cap, d_total, sc_max_spins);
         B2_CUDA(cudaEventRecord(ev[2], s));
         if (d_docs && d_tok_offsets)
             k_doc_token_offsets<<<std::max(1u, std::min(1024u, (n_docs + 256) / 256)), 256, 0, s>>>(cb, d_chunk_off, n_docs, d_tok_offsets);
@@ -1021,6 +1027,10 @@ b200bpe_status b200bpe_tokenizer_create_ex(b200bpe_ctx* c, const void* trie, siz
     t->hy_mul[0] = hy_mul[0]; t->hy_mul[1] = hy_mul[1];
     t->cold_mask = cold_mask;
     t->hot_entries = hot_entries;
+    if (opts->test_lookback_spins) {
+        t->sc_max_spins = opts->test_lookback_spins;
+        t->skip_first_tile = opts->test_lookback_spins < (1u << 20);
+    }
     if (opts->batch_slice_bytes >= 1024) t->batch_slice_bytes = opts->batch_slice_bytes;
     if (opts->encode_slice_bytes >= 1024) t->encode_slice_bytes = opts->encode_slice_bytes;
     cudaStream_t s = c->c.stream;
@@ -1292,7 +1302,7 @@ b200bpe_status b200bpe_encode_device_noalloc(b200bpe_tok* h, const uint8_t* d_by
     t->walk(d_bytes, n, nullptr, nullptr, 0, chunks, staging, counts, ctl + 2);
     const int grid_c = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)t->ctx->sm_count * 8, ntiles));
     k_scan_compact<<<grid_c, SC_THREADS, 0, s>>>(staging, counts, t->chunk, nullptr, 0, chunks, desc, ctl, chunk_off,
-                                                d_tokens_out, cap, total);
+                                                d_tokens_out, cap, total, t->sc_max_spins);
     B2_CUDA(cudaGetLastError());
     B2_CUDA(cudaMemcpyAsync(t->h_total, total, 8, cudaMemcpyDeviceToHost, s));
     B2_CUDA(cudaMemcpyAsync(t->h_total + 1, ctl, 8, cudaMemcpyDeviceToHost, s));

@@ -70,7 +70,7 @@ __device__ __forceinline__ void pt_st(unsigned long long* p, unsigned long long 
 __global__ void __launch_bounds__(PT_THREADS)
 k_pretokenize(ClassTables tab, const uint8_t* __restrict__ bytes, uint64_t n, uint8_t* __restrict__ out,
               unsigned long long* __restrict__ desc, uint32_t* __restrict__ ticket, uint32_t* __restrict__ status,
-              uint32_t tag) {
+              uint32_t tag, uint32_t max_spins) {
     __shared__ uint8_t sb[PT_BEFORE + PT_TILE + PT_AFTER];    // the bytes (0 outside the input)
     __shared__ uint8_t sc[PT_BEFORE + PT_TILE + PT_AFTER];    // class of the code point that starts here, PT_CONT on the others
     __shared__ uint32_t s_tile, s_carry, s_atr, s_aall;
@@ -170,7 +170,7 @@ k_pretokenize(ClassTables tab, const uint8_t* __restrict__ bytes, uint64_t n, ui
                     if (idx >= 0) { const unsigned long long d = pt_ld(desc + idx); hi = (uint32_t)(d >> 32); val = (uint32_t)d; }
                     const bool ready = (hi >> 2) == tag && (hi & 3u) != 0u;
                     if (__all_sync(0xFFFFFFFFu, ready)) break;
-                    if (++spins > PT_MAX_SPINS) { if (lane == 0) atomicExch(status, 2u); val = 0; hi = (tag << 2) | PT_PREFIX; break; }
+                    if (++spins > max_spins) { if (lane == 0) atomicExch(status, 2u); val = 0; hi = (tag << 2) | PT_PREFIX; break; }
                     __nanosleep(20);
                 }
                 // stop at the nearest predecessor that is a full prefix or is not all digits
@@ -314,6 +314,11 @@ using namespace b200bpe;
 extern "C" {
 
 b200bpe_status b200bpe_pretokenize_device(b200bpe_ctx* c, const uint8_t* d_bytes, uint64_t n, uint8_t* d_word_starts_out) {
+    return b200bpe_pretokenize_device_ex(c, d_bytes, n, d_word_starts_out, 0u);
+}
+
+b200bpe_status b200bpe_pretokenize_device_ex(b200bpe_ctx* c, const uint8_t* d_bytes, uint64_t n, uint8_t* d_word_starts_out,
+                                             uint32_t test_lookback_spins) {
     if (!c || ((!d_bytes || !d_word_starts_out) && n)) return B200BPE_ERR_BAD_ARG;
     if (n == 0) return B200BPE_OK;
     B2_CUDA(cudaSetDevice(c->c.device));
@@ -329,8 +334,14 @@ b200bpe_status b200bpe_pretokenize_device(b200bpe_ctx* c, const uint8_t* d_bytes
     uint32_t h_ctl[2] = {0, 0};
     cudaMemsetAsync(desc, 0, ntiles * 8, s);
     cudaMemsetAsync(ctl, 0, 8, s);
+    const bool stall = test_lookback_spins != 0u && test_lookback_spins < (1u << 20);
+    if (stall) {   // the tile ticket starts at 1: tile 0 is never worked on and never publishes its digits
+        static const uint32_t one = 1u;
+        cudaMemcpyAsync(ctl, &one, 4, cudaMemcpyHostToDevice, s);
+    }
     const int grid = (int)std::min<uint64_t>(ntiles, (uint64_t)c->c.sm_count * 8);
-    k_pretokenize<<<grid, PT_THREADS, 0, s>>>(tab, d_bytes, n, d_word_starts_out, desc, ctl, ctl + 1, 1u);
+    k_pretokenize<<<grid, PT_THREADS, 0, s>>>(tab, d_bytes, n, d_word_starts_out, desc, ctl, ctl + 1, 1u,
+                                              test_lookback_spins ? test_lookback_spins : PT_MAX_SPINS);
     cudaError_t e = cudaMemcpyAsync(h_ctl, ctl, 8, cudaMemcpyDeviceToHost, s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
     cudaFree(desc);

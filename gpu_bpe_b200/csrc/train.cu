@@ -282,6 +282,8 @@ b200bpe_status Trainer::init_state() {
     h_state->incremental = incremental ? 1u : 0u;
     h_state->recount = 1u;
     h_state->table = table;
+    h_state->lb_max_spins = opts.test_lookback_spins ? opts.test_lookback_spins : LOOKBACK_MAX_SPINS;
+    h_state->first_ticket = opts.test_first_tile ? 1u : 0u;
     h_state->scan_from = 0u;            // the first arg-max scans the table
     h_state->presetup_at = 0xFFFFFFFFu;
     h_state->cand_tau = 0xFFFFFFFFu;

@@ -422,7 +422,7 @@ __device__ __forceinline__ void setup_merge(DevState* st, const DevState* rd, ui
     st->merges_done = md + 1u;
     if (md + 1u >= rd->merges_target) st->target_hit = 1u;
     st->k3_epoch = rd->epoch;
-    st->ticket = 0u;
+    st->ticket = rd->first_ticket;
     st->active = 1u;
     // Incremental table: a merge of two equal symbols collapses whole runs, which the local
     // update rule does not cover; the table is emptied and rebuilt by a full count instead.
@@ -627,38 +627,6 @@ __device__ __forceinline__ unsigned long long ld_desc(const unsigned long long* 
 }
 __device__ __forceinline__ void st_desc(unsigned long long* p, unsigned long long v) {
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-
-// Exclusive offset of `tile` = sum of the kept counts of all earlier tiles (one warp).
-// Bounded wait: if a predecessor never shows up, *timed_out is set and 0 is returned.
-__device__ __forceinline__ uint32_t lookback(const unsigned long long* __restrict__ desc, uint32_t tile, uint32_t tag,
-                                             int lane, bool* timed_out) {
-    uint32_t excl = 0u, spins = 0u;
-    int pos = (int)tile - 1;
-    for (;;) {
-        const int idx = pos - lane;
-        uint32_t hi = (tag << 2) | DESC_PREFIX;  // positions before tile 0 act as a zero prefix
-        uint32_t val = 0u;
-        for (;;) {
-            if (idx >= 0) {
-                const unsigned long long d = ld_desc(desc + idx);
-                hi = (uint32_t)(d >> 32);
-                val = (uint32_t)d;
-            }
-            const bool ready = ((hi >> 2) == tag) && (hi & 3u) != 0u;
-            if (__all_sync(0xFFFFFFFFu, ready)) break;
-            if (++spins > LOOKBACK_MAX_SPINS) { *timed_out = true; return 0u; }
-            __nanosleep(20);
-        }
-        const uint32_t pmask = __ballot_sync(0xFFFFFFFFu, (hi & 3u) == DESC_PREFIX);
-        const int first = pmask ? (__ffs(pmask) - 1) : 32;  // nearest predecessor holding a full prefix
-        uint32_t contrib = (lane <= first) ? val : 0u;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xFFFFFFFFu, contrib, o);
-        excl += contrib;
-        if (pmask) return excl;
-        pos -= 32;
-    }
 }
 
 // Incremental table maintenance, the rare path of k_merge_compact: called by a whole warp for a row
@@ -894,6 +862,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
     const uint32_t tag = (e + 1u) & 0x3FFFFFFFu;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const bool deltas = INCR && st->recount == 0u;
+    const uint32_t lb_max_spins = st->lb_max_spins;
     const uint32_t logC = st->table_log2;
     if (table == nullptr) table = st->table;
     auto snapshot = [&](uint32_t v) { return (v & TOKEN_MASK) == NW ? ((v & WORD_START_BIT) | A) : v; };
@@ -1210,7 +1179,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                         ready = ready && ((hi[k] >> 2) == tag) && (hi[k] & 3u) != 0u;
                     }
                     if (__all_sync(0xFFFFFFFFu, ready)) break;
-                    if (spins > LOOKBACK_MAX_SPINS) { timed_out = true; break; }
+                    if (spins > lb_max_spins) { timed_out = true; break; }
                     __nanosleep(20);
                 }
                 // within the thread: add values, nearest first, up to and including the first full prefix

@@ -31,6 +31,7 @@ class TrieTokenizer:
         o.struct_size = C.sizeof(_lib.TokOpts)
         o.chunk_size = int(options.get("chunkSize") or 0)
         o.layout = _lib.TRIE_LAYOUTS[options.get("layout") or "auto"]
+        o.test_lookback_spins = int(options.get("testLookbackSpins") or 0)
         o.batch_slice_bytes = int(options.get("batchSliceBytes") or 0)
         o.encode_slice_bytes = int(options.get("encodeSliceBytes") or 0)
         st = _lib.lib().b200bpe_tokenizer_create_ex(engine.ctx, buf.ctypes.data, buf.size, C.byref(o), C.byref(h))

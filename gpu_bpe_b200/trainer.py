@@ -51,9 +51,11 @@ class TrainerSession:
         self._keep = []
 
     @staticmethod
-    def _opts(target_vocab_size, first_token_id, compat_mode, batch_merges, table_log2, flags, exchange_cap=0):
+    def _opts(target_vocab_size, first_token_id, compat_mode, batch_merges, table_log2, flags, exchange_cap=0,
+              test_lookback_spins=0, test_first_tile=0):
         o = _lib.TrainOpts()
         o.exchange_cap = exchange_cap
+        o.test_lookback_spins, o.test_first_tile = test_lookback_spins, test_first_tile
         o.struct_size = C.sizeof(_lib.TrainOpts)
         o.target_vocab_size, o.first_token_id = target_vocab_size, first_token_id
         o.batch_merges, o.table_log2, o.flags = batch_merges, table_log2, flags
@@ -63,8 +65,9 @@ class TrainerSession:
     @classmethod
     def create(cls, engine, data: np.ndarray, word_starts, *, target_vocab_size=4096, first_token_id=256,
                compat_mode="literal", batch_merges=BATCH_SIZE, table_log2=0, flags=0, device_pointers=False,
-               n: int | None = None, exchange_cap=0):
-        o = cls._opts(target_vocab_size, first_token_id, compat_mode, batch_merges, table_log2, flags, exchange_cap)
+               n: int | None = None, exchange_cap=0, test_lookback_spins=0, test_first_tile=0):
+        o = cls._opts(target_vocab_size, first_token_id, compat_mode, batch_merges, table_log2, flags, exchange_cap,
+                      test_lookback_spins, test_first_tile)
         h = C.c_void_p()
         L = _lib.lib()
         if device_pointers:
@@ -83,7 +86,8 @@ class TrainerSession:
     @classmethod
     def from_symbols(cls, engine, symbols: np.ndarray, **kw):
         o = cls._opts(kw.get("target_vocab_size", 4096), kw.get("first_token_id", 256), kw.get("compat_mode", "literal"),
-                      kw.get("batch_merges", BATCH_SIZE), kw.get("table_log2", 0), kw.get("flags", 0))
+                      kw.get("batch_merges", BATCH_SIZE), kw.get("table_log2", 0), kw.get("flags", 0), 0,
+                      kw.get("test_lookback_spins", 0), kw.get("test_first_tile", 0))
         sym = np.ascontiguousarray(symbols, np.uint32)
         h = C.c_void_p()
         _lib.check(_lib.lib().b200bpe_trainer_create_from_symbols(engine.ctx, sym.ctypes.data if sym.size else None,

@@ -75,6 +75,12 @@ typedef struct {
     uint32_t flags;             /* B200BPE_FLAG_* */
     uint32_t exchange_cap;      /* tests only: first bucket size of the NCCL exchange in slots (0 = default), to reach
                                    the bucket-overflow path with a small corpus */
+    /* tests only: prove that a device-side wait that can never be satisfied ends by itself.  test_lookback_spins
+       (0 = default, about four million) is the number of polls after which a look-back gives up;
+       test_first_tile = 1 makes the merge kernel skip tile 0, so that nobody ever publishes the count every
+       other tile waits for: the run then ends with B200BPE_ERR_LOOKBACK_TIMEOUT instead of a merge list. */
+    uint32_t test_lookback_spins;
+    uint32_t test_first_tile;
 } b200bpe_train_opts;
 
 /* Progress payload, one call per batch: the fields of trainer.js:306-314. */
@@ -187,7 +193,9 @@ typedef struct {
     uint32_t struct_size;        /* sizeof(b200bpe_tok_opts) */
     uint32_t chunk_size;         /* tokenizer.js:67-68 options.chunkSize; 0 = the reference rule */
     uint32_t layout;             /* B200BPE_TRIE_*; a layout the trie does not fit falls through to the next one */
-    uint32_t reserved;
+    uint32_t test_lookback_spins; /* tests only: polls after which the look-back of the compaction gives up (0 = default);
+                                    a value below 2^20 also makes the compaction skip tile 0, which no other tile
+                                    can then get past: the call ends with B200BPE_ERR_LOOKBACK_TIMEOUT */
     uint64_t batch_slice_bytes;  /* 0 = default; at least 1024 */
     uint64_t encode_slice_bytes; /* 0 = default; at least 1024 (rounded down to whole chunks) */
 } b200bpe_tok_opts;
@@ -243,6 +251,11 @@ b200bpe_status b200bpe_pretokenize(const uint8_t* bytes, uint64_t n, uint8_t* wo
  * across tiles by a decoupled look-back scan. */
 b200bpe_status b200bpe_pretokenize_device(b200bpe_ctx*, const uint8_t* d_bytes, uint64_t n, uint8_t* d_word_starts_out);
 b200bpe_status b200bpe_pretokenize_gpu(b200bpe_ctx*, const uint8_t* bytes, uint64_t n, uint8_t* word_starts_out);
+/* Tests only (no counterpart in the reference): the device function with the number of polls after which its
+ * look-back gives up (0 = default).  A value below 2^20 also makes the kernel skip tile 0, whose digit count no
+ * other tile can then obtain: the call ends with B200BPE_ERR_LOOKBACK_TIMEOUT, which proves that the wait is bounded. */
+b200bpe_status b200bpe_pretokenize_device_ex(b200bpe_ctx*, const uint8_t* d_bytes, uint64_t n, uint8_t* d_word_starts_out,
+                                             uint32_t test_lookback_spins);
 
 /* ── token file export: replaces the ".bin" writer of the Export tab (src/ui/export-controller.js:4,235-248) ──
  * Host code.  Layout: u32 LE {0x44584654 'DXFT', vocabSize, tokenCount, vocabJsonBytes}, the tokens as u32 LE,

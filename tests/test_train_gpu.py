@@ -29,10 +29,12 @@ def test_known_answers(engine, case, mode):
     assert early
 
 
-# sizes either side of every structural edge: one 16-byte vector, one warp row (128), one tile
-# (4096), the reference's workgroup (256) and its parallel/sequential scan switch (65,536)
-@pytest.mark.parametrize("n", [1, 2, 3, 4, 5, 127, 128, 129, 255, 256, 257, 4095, 4096, 4097, 8191, 8193, 65535, 65536,
-                               65537, 200_001])
+# sizes either side of every structural edge: one 16-byte vector, one warp row (128), one span (512),
+# one sub-tile (4,096), one, two and three tiles (12,288 each), the reference's workgroup (256) and its
+# parallel/sequential scan switch (65,536)
+@pytest.mark.parametrize("n", [1, 2, 3, 4, 5, 127, 128, 129, 255, 256, 257, 511, 513, 4095, 4096, 4097, 8191, 8193,
+                               12287, 12288, 12289, 24575, 24576, 24577, 36863, 36864, 36865, 65535, 65536, 65537,
+                               200_001])
 @pytest.mark.parametrize("mode", ["literal", "fixed"])
 def test_random_symbols_match_oracle(engine, n, mode):
     rng = np.random.default_rng(n + 17 * (mode == "fixed"))
@@ -42,6 +44,24 @@ def test_random_symbols_match_oracle(engine, n, mode):
     assert merges == want["merges"].tolist()
     assert early == want["early_stop"]
     assert final == want["symbols"].tolist()
+
+
+@pytest.mark.parametrize("mode", ["literal", "fixed"])
+@pytest.mark.parametrize("drop", [0, 1, 2, 3, 4, 5, 6, 7])
+def test_literal_limit_at_every_alignment(engine, drop):
+    """Literal mode copies only the inputs below N - count: the first merge's count is set here so that the limit,
+    and with it the end of the copy-out, lands on each of the four alignments of a 16-byte store, in the last tile
+    of three."""
+    n = 3 * 12288 - 5
+    sym = np.full(n, 120 | 0x10000, np.uint32)  # every filler symbol starts a word: no pairs among them
+    k = 40 + drop                               # k occurrences of the pair (a, b), apart from one another
+    pos = np.arange(k) * 700 + 17
+    sym[pos] = 97 | 0x10000
+    sym[pos + 1] = 98
+    want = O.train(sym, 3, "literal", threads=2)
+    assert want["merges"].tolist() == [[97, 98, 256, k]] and want["early_stop"]
+    merges, early, final = run_gpu(engine, sym, 3, "literal")
+    assert merges == want["merges"].tolist() and final == want["symbols"].tolist() and early
 
 
 @pytest.mark.parametrize("mode", ["literal", "fixed"])
