@@ -98,6 +98,11 @@ SIGNATURES = {
     "b200bpe_encode_device_noalloc": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64, u64p]),
     "b200bpe_tokenizer_last_ms": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "b200bpe_tokenizer_destroy": (None, [C.c_void_p]),
+    "b200bpe_replay_create": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(C.c_void_p)]),
+    "b200bpe_replay_encode": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64, u64p]),
+    "b200bpe_replay_encode_device": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64, u64p]),
+    "b200bpe_replay_last_rounds": (C.c_int32, [C.c_void_p, u32p]),
+    "b200bpe_replay_destroy": (None, [C.c_void_p]),
     "b200bpe_pretokenize": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_void_p]),
     "b200bpe_pretokenize_device": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]),
     "b200bpe_pretokenize_device_ex": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint32]),

@@ -17,7 +17,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libb200bpe.so")
 SYNTH = os.path.join(PKG, "libb200bpe_synth.so")
 
-CUDA_SOURCES = ["api.cu", "train.cu", "encode.cu", "trie.cpp", "pretok.cpp", "pretok_gpu.cu", "export.cpp"]
+CUDA_SOURCES = ["api.cu", "train.cu", "encode.cu", "replay.cu", "trie.cpp", "pretok.cpp", "pretok_gpu.cu", "export.cpp"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "-shared", "-cudart", "static"]
 

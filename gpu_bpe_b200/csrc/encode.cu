@@ -51,13 +51,15 @@ constexpr uint32_t CK_MIN_LOG2 = 11, CK_MAX_LOG2 = 14;  // slots per sub-table
 constexpr uint32_t CK_HAS_TOKEN = 1u << 16, CK_LEAF = 1u << 17, CK_INDEX = 0xFFFFu, CK_VALUE = 0x3FFFFu;
 constexpr uint32_t CK_EMPTY = 0xFFFFFFFFu;
 
-// hybrid layout: 4-byte entries  remainder(13) << 19 | leaf << 18 | has_token << 17 | index(17)
+// hybrid layout: 4-byte entries  remainder(13) << 19 | cold << 18 | leaf << 17 | index(17); a node ends a token iff
+// its index is at most the largest token id (token nodes are numbered by their ids, the others follow);
+// cold = some child of the node is in the global table only
 constexpr int HY_THREADS = 512;
 constexpr int HY_CTAS = 3;
 constexpr uint32_t HY_BUCKET_LOG2 = 12;                       // buckets per sub-table; a bucket holds two entries
 constexpr uint32_t HY_KEY_BITS = 25, HY_KEY_MASK = (1u << HY_KEY_BITS) - 1u;
 constexpr uint32_t HY_REM_SHIFT = HY_KEY_BITS - HY_BUCKET_LOG2;   // 13 remainder bits
-constexpr uint32_t HY_INDEX = 0x1FFFFu, HY_HAS_TOKEN = 1u << 17, HY_LEAF = 1u << 18;
+constexpr uint32_t HY_INDEX = 0x1FFFFu, HY_LEAF = 1u << 17, HY_COLD = 1u << 18;
 constexpr uint32_t HY_ROOT2 = 0x1FF00u;                       // pseudo parents 0x1FF00 | b0 of the two-byte first step
 constexpr uint32_t HY_MAX_INDEX = HY_ROOT2;                   // real node indices stay below
 constexpr uint32_t HY_HOT_WORDS = 2u * (1u << HY_BUCKET_LOG2) * 2u;   // 16,384 entries = 64 KB
@@ -69,7 +71,7 @@ struct TrieHybrid {
     uint32_t mul[2];         // odd multipliers of the two hash functions (modulo 2^25)
     const uint2* cold;       // open addressing: {key, value in the 4-byte entry's value format}
     uint32_t cold_mask;
-    const uint32_t* cold_bits;  // bit per node index: some child of the node is only in the cold table
+    uint32_t max_token;      // indices up to this one end a token
 };
 
 struct TrieDev {
@@ -319,10 +321,9 @@ k_trie_walk_hybrid(TrieHybrid t, const uint8_t* __restrict__ bytes, uint64_t n, 
             nv = (e1.x >> 19) == r1 ? e1.x : nv;
             nv = (e1.y >> 19) == r1 ? e1.y : nv;
             bool hit = (nv & HY_INDEX) != HY_INDEX && (two || !fresh);   // an empty entry is all ones
-            if (!hit && !fresh) {
-                // some of this node's children may live in the global table only
-                const uint32_t vi = v & HY_INDEX;
-                if ((__ldg(t.cold_bits + (vi >> 5)) >> (vi & 31u)) & 1u) {
+            if (!hit && !fresh && (v & HY_COLD)) {
+                // some of this node's children live in the global table only
+                {
                     const uint32_t hh = key * 0x9E3779B1u;
                     uint32_t slot = (hh ^ (hh >> 15)) & t.cold_mask;
                     for (;;) {
@@ -334,14 +335,14 @@ k_trie_walk_hybrid(TrieHybrid t, const uint8_t* __restrict__ bytes, uint64_t n, 
                 }
             }
             if (fresh) {   // what the first byte alone is worth
-                have = n1 != T_MISS && (n1 & HY_HAS_TOKEN) != 0u;
+                have = (n1 & HY_INDEX) <= t.max_token;   // T_MISS has an index above every token id
                 last = n1 & HY_INDEX;
                 l = p + 1u;
             }
             if (hit) {
                 v = nv;
                 w = fresh ? p + 2u : w + 1u;
-                if (nv & HY_HAS_TOKEN) { have = true; last = nv & HY_INDEX; l = w; }
+                if ((nv & HY_INDEX) <= t.max_token) { have = true; last = nv & HY_INDEX; l = w; }
             }
             const bool ends = !hit || (nv & HY_LEAF) != 0u || w >= len;
             if (ends) {
@@ -537,8 +538,7 @@ struct Tokenizer {
     bool hybrid = false;
     uint32_t* d_hot = nullptr;       // shared-memory image: the bucketed cuckoo table, then the root's 256 children
     uint2* d_cold = nullptr;
-    uint32_t* d_cold_bits = nullptr;
-    uint32_t hy_mul[2] = {1u, 1u}, cold_mask = 0, hot_entries = 0;
+    uint32_t hy_mul[2] = {1u, 1u}, cold_mask = 0, hot_entries = 0, max_token = 0;
     uint32_t sc_max_spins = SC_MAX_SPINS;       // polls after which the compaction's look-back gives up
     bool skip_first_tile = false;               // test of that bounded wait: tile 0 is never worked on
     uint64_t batch_slice_bytes = 32ull << 20;   // host batches above twice this are encoded slice by slice
@@ -561,7 +561,7 @@ struct Tokenizer {
 
     ~Tokenizer() {
         if (ctx) cudaSetDevice(ctx->device);
-        cudaFree(d_trans); cudaFree(d_cuckoo); cudaFree(d_hot); cudaFree(d_cold); cudaFree(d_cold_bits); cudaFree(d_in); cudaFree(d_staging);
+        cudaFree(d_trans); cudaFree(d_cuckoo); cudaFree(d_hot); cudaFree(d_cold); cudaFree(d_in); cudaFree(d_staging);
         cudaFree(d_counts); cudaFree(d_chunk_off); cudaFree(d_out); cudaFree(d_doc_off); cudaFree(d_chunk_base);
         cudaFree(d_tok_off); cudaFree(d_desc); cudaFree(d_ctl); cudaFree(d_total);
         if (h_total) cudaFreeHost(h_total);
@@ -606,7 +606,7 @@ struct Tokenizer {
         TrieDev t{d_trans, trans_mask, d_cuckoo, ck_log2, {ck_mul[0], ck_mul[1], ck_mul[2]}, root};
         const uint64_t n_static = (n + chunk - 1) / chunk;
         if (hybrid) {
-            TrieHybrid th{d_hot, {hy_mul[0], hy_mul[1]}, d_cold, cold_mask, d_cold_bits};
+            TrieHybrid th{d_hot, {hy_mul[0], hy_mul[1]}, d_cold, cold_mask, max_token};
             const int grid = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)ctx->sm_count * HY_CTAS, (max_chunks + HY_THREADS - 1) / HY_THREADS));
             k_trie_walk_hybrid<<<grid, HY_THREADS, HY_SMEM_BYTES, s>>>(th, d_bytes, n, chunk, d_docs, cb, n_docs, n_static, staging, counts, ticket);
         } else if (ck_d == 0) {
@@ -750,9 +750,8 @@ b200bpe_status b200bpe_tokenizer_create_ex(b200bpe_ctx* c, const void* trie, siz
     // Device numbering: a node that ends a token is numbered by its token id, the others follow
     // after the largest id, the root comes last.
     std::vector<uint32_t> dev_index(node_count, 0u);
-    uint32_t root_index = 0;
+    uint32_t root_index = 0, max_tok = 0;
     {
-        uint32_t max_tok = 0;
         bool any = false;
         for (uint32_t i = 1; i < node_count; i++) {
             const uint32_t tk = nodes[(size_t)i * 3 + 2];
@@ -763,7 +762,7 @@ b200bpe_status b200bpe_tokenizer_create_ex(b200bpe_ctx* c, const void* trie, siz
             }
         }
         std::vector<uint8_t> seen((size_t)max_tok + 1, 0);
-        uint32_t next_free = any ? max_tok + 1 : 0;
+        uint32_t next_free = any ? max_tok + 1 : 1;   // (no token at all: index 0 stays unused, so that "index <= largest token id" holds for no node)
         for (uint32_t i = 1; i < node_count; i++) {
             const uint32_t tk = nodes[(size_t)i * 3 + 2];
             if (tk != INVALID_TOKEN) {
@@ -862,9 +861,7 @@ b200bpe_status b200bpe_tokenizer_create_ex(b200bpe_ctx* c, const void* trie, siz
     bool hybrid = false;
     const bool want_hybrid = opts->layout == B200BPE_TRIE_HYBRID || (opts->layout == B200BPE_TRIE_AUTO && ck_d == 0);
     if (want_hybrid && ck_d == 0 && root_index < HY_MAX_INDEX) {
-        auto pack = [&](uint32_t node) {
-            return dev_index[node] | (is_token(node) ? HY_HAS_TOKEN : 0u) | (is_leaf(node) ? HY_LEAF : 0u);
-        };
+        auto pack = [&](uint32_t node) { return dev_index[node] | (is_leaf(node) ? HY_LEAF : 0u); };   // the cold flag is added at the end
         // children of a node: first of equal symbols only, as above
         auto for_children = [&](uint32_t node, auto&& fn) {
             const uint32_t fc = nodes[(size_t)node * 3], nc = nodes[(size_t)node * 3 + 1] & 0xFFFFu;
@@ -992,6 +989,13 @@ b200bpe_status b200bpe_tokenizer_create_ex(b200bpe_ctx* c, const void* trie, siz
                 cold[slot] = make_uint2(deep[i].key, deep[i].value);
                 cold_bits[deep[i].parent >> 5] |= 1u << (deep[i].parent & 31u);
             }
+            // every stored value learns whether the node it names has cold children
+            auto with_cold = [&](uint32_t value) {
+                const uint32_t idx = value & HY_INDEX;
+                return (idx != HY_INDEX && ((cold_bits[idx >> 5] >> (idx & 31u)) & 1u)) ? (value | HY_COLD) : value;
+            };
+            for (uint32_t& wv : hot) if (wv != 0xFFFFFFFFu) wv = with_cold(wv);
+            for (uint2& c2 : cold) if (c2.x != T_EMPTY_KEY) c2.y = with_cold(c2.y);
             hy_mul[0] = mul[0]; hy_mul[1] = mul[1];
             hybrid = true;
         }
@@ -1027,6 +1031,7 @@ b200bpe_status b200bpe_tokenizer_create_ex(b200bpe_ctx* c, const void* trie, siz
     t->hy_mul[0] = hy_mul[0]; t->hy_mul[1] = hy_mul[1];
     t->cold_mask = cold_mask;
     t->hot_entries = hot_entries;
+    t->max_token = max_tok;
     if (opts->test_lookback_spins) {
         t->sc_max_spins = opts->test_lookback_spins;
         t->skip_first_tile = opts->test_lookback_spins < (1u << 20);
@@ -1041,8 +1046,6 @@ b200bpe_status b200bpe_tokenizer_create_ex(b200bpe_ctx* c, const void* trie, siz
         B2_TRY(cudaMemcpyAsync(t->d_hot, hot.data(), hot.size() * 4, cudaMemcpyHostToDevice, s));
         B2_TRY(cudaMalloc(&t->d_cold, cold.size() * 8));
         B2_TRY(cudaMemcpyAsync(t->d_cold, cold.data(), cold.size() * 8, cudaMemcpyHostToDevice, s));
-        B2_TRY(cudaMalloc(&t->d_cold_bits, cold_bits.size() * 4));
-        B2_TRY(cudaMemcpyAsync(t->d_cold_bits, cold_bits.data(), cold_bits.size() * 4, cudaMemcpyHostToDevice, s));
         B2_TRY(cudaFuncSetAttribute(k_trie_walk_hybrid, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)HY_SMEM_BYTES));
     } else if (ck_d == 0) {
         B2_TRY(cudaMalloc(&t->d_trans, trans.size() * 8));

@@ -109,11 +109,17 @@ k_route(DevState* __restrict__ st, PairSlot* __restrict__ table, PeerBufs pb, ui
     const bool full = st->recount != 0u;   // the count kernel of this iteration has just counted everything
     const uint32_t C = 1u << st->table_log2;
     const uint32_t n = full ? C : min(__ldcg(&st->dlist_n), DLIST_CAP);
+    // A merge changes a few thousand pairs: only as many CTAs as that needs take part (and are waited for).
+    // (`dlist_n` is put back to zero by the last of them, when every CTA that takes part has read it; a CTA
+    // that reads the zero later has a number beyond `need` either way.)
+    const uint32_t need = full ? gridDim.x : max(1u, min(gridDim.x, (n + 4u * PX_THREADS - 1u) / (4u * PX_THREADS)));
+    if (blockIdx.x >= need) return;
     const uint32_t* __restrict__ dlist = st->dlist;
     uint4* __restrict__ t4 = reinterpret_cast<uint4*>(table);
     const int lane = threadIdx.x & 31;
     uint32_t live = 0u;
-    for (uint32_t i0 = blockIdx.x * PX_THREADS + (threadIdx.x & ~31u); i0 < n; i0 += gridDim.x * PX_THREADS) {
+    bool sent = false;
+    for (uint32_t i0 = blockIdx.x * PX_THREADS + (threadIdx.x & ~31u); i0 < n; i0 += need * PX_THREADS) {
         const uint32_t i = i0 + lane;
         uint32_t slot = 0u;
         uint4 q = make_uint4(0u, 0u, 0u, 0u);
@@ -136,6 +142,7 @@ k_route(DevState* __restrict__ st, PairSlot* __restrict__ table, PeerBufs pb, ui
             if (d < pb.cap) {
                 uint4* inbox = reinterpret_cast<uint4*>(pb.base[o] + PX_INBOX_OFF) + (size_t)pb.rank * pb.cap;
                 inbox[d] = make_uint4(q.x, q.y, q.z, 0u);
+                sent = true;
             } else {
                 atomicCAS(&st->status, (uint32_t)DS_OK, (uint32_t)DS_BUCKET_FULL);
             }
@@ -147,9 +154,9 @@ k_route(DevState* __restrict__ st, PairSlot* __restrict__ table, PeerBufs pb, ui
         for (int o = 16; o > 0; o >>= 1) live += __shfl_xor_sync(0xFFFFFFFFu, live, o);
         if (lane == 0 && live) atomicAdd(&st->occupied, live);
     }
-    __threadfence_system();   // this thread's entries are out before its CTA is counted as done
+    if (sent) __threadfence_system();   // this thread's entries are out before its CTA is counted as done
     __syncthreads();
-    if (threadIdx.x == 0) s_last = (atomicAdd(&st->xdone[0], 1u) == gridDim.x - 1u) ? 1u : 0u;
+    if (threadIdx.x == 0) s_last = (atomicAdd(&st->xdone[0], 1u) == need - 1u) ? 1u : 0u;
     __syncthreads();
     if (!s_last) return;
     __threadfence_system();

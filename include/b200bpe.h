@@ -240,6 +240,22 @@ b200bpe_status b200bpe_encode_device_noalloc(b200bpe_tok*, const uint8_t* d_byte
 b200bpe_status b200bpe_tokenizer_last_ms(b200bpe_tok*, double* walk_ms, double* compact_ms);
 void b200bpe_tokenizer_destroy(b200bpe_tok*);
 
+/* ── merge-replay encoding: replaces TokenizerManager.encode (src/ui/tokenizer-manager.js:13-61) ──
+ * The reference's other encoder: one token per byte, then every merge rule {a, b, new_id} applied in the order
+ * it was learned, each as one left-to-right pass over the whole token list (no word boundaries, no chunks; with
+ * a == b a run pairs up from the left).  merges: 3 words per rule.  The list must be one a trainer could have
+ * produced: every rule makes an id of its own (not a byte value) and uses only ids that earlier rules made;
+ * other lists are refused with B200BPE_ERR_BAD_ARG.  No merges: the bytes are the tokens (:21-25). */
+typedef struct b200bpe_replay b200bpe_replay;
+b200bpe_status b200bpe_replay_create(b200bpe_ctx*, const uint32_t* merges, uint32_t n_merges, b200bpe_replay** out);
+b200bpe_status b200bpe_replay_encode(b200bpe_replay*, const uint8_t* bytes, uint64_t n, uint32_t* tokens_out, uint64_t cap,
+                                     uint64_t* n_tokens_out);
+b200bpe_status b200bpe_replay_encode_device(b200bpe_replay*, const uint8_t* d_bytes, uint64_t n, uint32_t* d_tokens_out,
+                                            uint64_t cap, uint64_t* n_tokens_out);
+/* Rounds (rules that found their pair) of the last call; diagnostics. */
+b200bpe_status b200bpe_replay_last_rounds(b200bpe_replay*, uint32_t* rounds_out);
+void b200bpe_replay_destroy(b200bpe_replay*);
+
 /* ── pre-tokeniser: replaces PreTokenizer.preTokenizeBytes (src/wasm/pre_tokenizer.mjs:459-509) ──
  * Host code.  GPT-4-style word starts over code-point classes; the input must already be NFC
  * (the reference normalises with a closed-source WASM library first, pre_tokenizer.mjs:465).

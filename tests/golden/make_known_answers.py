@@ -38,8 +38,25 @@ CASES = [
      "fixed": {"merges": [], "symbols": ["0x10061", "0x10062", "0x10061", "0x10062"]}},
 ]
 
+# Merge-replay encoding (TokenizerManager.encode, src/ui/tokenizer-manager.js:13-61), worked out by hand from
+# that loop: one token per byte, then every rule in learned order, each one left-to-right pass that steps over
+# both tokens of a match.
+REPLAY_CASES = [
+    {"text": "aaa", "merges": [[97, 97, 256]], "tokens": [256, 97]},                      # pairs from the left, the odd one stays
+    {"text": "aaaa", "merges": [[97, 97, 256]], "tokens": [256, 256]},                    # not one token, unlike the trainer's merge
+    {"text": "aaaaa", "merges": [[97, 97, 256], [256, 256, 257]], "tokens": [257, 97]},
+    {"text": "abab", "merges": [[97, 98, 256], [256, 256, 257]], "tokens": [257]},
+    {"text": "abc", "merges": [[98, 99, 256], [97, 98, 257]], "tokens": [97, 256]},       # the earlier rule takes the b
+    {"text": "abc", "merges": [[97, 98, 256], [98, 99, 257]], "tokens": [256, 99]},
+    {"text": "xyz", "merges": [[97, 98, 256]], "tokens": [120, 121, 122]},                # no rule applies
+    {"text": "", "merges": [[97, 98, 256]], "tokens": []},
+    {"text": "ab", "merges": [], "tokens": [97, 98]},                                     # no merges: byte level (:21-25)
+    {"text": "a b a b", "merges": [[97, 32, 256], [256, 98, 257]], "tokens": [257, 32, 257]},           # no word boundaries on this path
+    {"text": "é", "merges": [[195, 169, 256]], "tokens": [256]},                          # bytes of the UTF-8 encoding
+]
+
 if __name__ == "__main__":
     out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "known_answers.json")
     with open(out, "w") as f:
-        json.dump({"word_start_marker": "|", "cases": CASES}, f, indent=1)
+        json.dump({"word_start_marker": "|", "cases": CASES, "replay": REPLAY_CASES}, f, indent=1, ensure_ascii=True)
     print(out)

@@ -123,3 +123,40 @@ def test_pretokenizer_rules():
     assert starts("a\nb") == [0, 1, 2]                          # newline isolates
     assert starts("hi!!") == [0, 2]                             # punctuation run is one word
     assert starts("ğa“b") == [0, 3, 6]                          # multi-byte letter / punctuation by code point
+
+
+def test_replay_known_answers():
+    """The merge-replay oracle (oracle/replay_oracle.cpp) against the hand-derived cases and a literal Python
+    transcription of the loop of src/ui/tokenizer-manager.js:45-58."""
+    import json
+    import os
+    from tests.helpers import GOLDEN
+    with open(os.path.join(GOLDEN, "known_answers.json")) as f:
+        cases = json.load(f)["replay"]
+    for c in cases:
+        data = np.frombuffer(c["text"].encode("utf-8"), np.uint8)
+        assert O.replay_encode(data, c["merges"]).tolist() == c["tokens"], c["text"]
+
+    def literal(tokens, merges):
+        for a, b, new in merges:
+            if len(tokens) < 2:
+                break
+            out, i = [], 0
+            while i < len(tokens):
+                if i + 1 < len(tokens) and tokens[i] == a and tokens[i + 1] == b:
+                    out.append(new)
+                    i += 2
+                else:
+                    out.append(tokens[i])
+                    i += 1
+            tokens = out
+        return tokens
+
+    rng = np.random.default_rng(3)
+    for trial in range(20):
+        data = rng.integers(97, 100, int(rng.integers(0, 200)), dtype=np.uint8)
+        merges, ids = [], [97, 98, 99]
+        for r in range(int(rng.integers(0, 12))):
+            merges.append([int(rng.choice(ids)), int(rng.choice(ids)), 256 + r])
+            ids.append(256 + r)
+        assert O.replay_encode(data, merges).tolist() == literal(data.tolist(), merges), trial

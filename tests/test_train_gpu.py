@@ -46,7 +46,6 @@ def test_random_symbols_match_oracle(engine, n, mode):
     assert final == want["symbols"].tolist()
 
 
-@pytest.mark.parametrize("mode", ["literal", "fixed"])
 @pytest.mark.parametrize("drop", [0, 1, 2, 3, 4, 5, 6, 7])
 def test_literal_limit_at_every_alignment(engine, drop):
     """Literal mode copies only the inputs below N - count: the first merge's count is set here so that the limit,
