@@ -854,11 +854,4 @@ b200bpe_status b200bpe_train(b200bpe_ctx* c, const uint8_t* bytes, const uint8_t
 
 }  // extern "C"
 
-#ifdef B200BPE_PHASES
-// Diagnostics build only: read (and clear) the per-phase cycle counters of k_merge_compact.
-extern "C" int b200bpe_debug_phases(unsigned long long out[8]) {
-    if (cudaMemcpyFromSymbol(out, b200bpe::g_phase_cycles, 64) != cudaSuccess) return 1;
-    unsigned long long zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    return cudaMemcpyToSymbol(b200bpe::g_phase_cycles, zero, 64) != cudaSuccess;
-}
-#endif
+

@@ -821,13 +821,6 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t pari
 // cannot overlap, so a dropped symbol's successor is always kept and three symbols of look-ahead
 // settle everything); a merge with a == b collapses whole runs (train.wgsl:482-497 on a run
 // "aaaa" yields one symbol), so it empties the table here and the next merge counts from scratch.
-#ifdef B200BPE_PHASES
-// Diagnostics build only: SM cycles that thread 0 of every CTA spent per phase of a tile.
-__device__ unsigned long long g_phase_cycles[8];
-#define PHASE_MARK(k) do { if (threadIdx.x == 0) { const long long t_ = clock64(); ph[k] += t_ - ph_last; ph_last = t_; } } while (0)
-#else
-#define PHASE_MARK(k) do {} while (0)
-#endif
 
 // SHARD (sharded runs with the peer-memory exchange): the deltas go into the local delta table for
 // the route kernel, and a merge of two equal symbols empties this rank's table of owned pairs.
@@ -909,9 +902,6 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
         }
     }
     __syncthreads();
-#ifdef B200BPE_PHASES
-    long long ph[8] = {0, 0, 0, 0, 0, 0, 0, 0}, ph_last = clock64();
-#endif
 #pragma unroll
     for (int b = 0; b < MC_NBUF - 1; b++)
         if (s_tid[b] < ntiles) fetch_tile(s_tid[b], b);
@@ -921,10 +911,8 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
         const uint32_t cb = j % MC_NBUF, pb = (j + MC_NBUF - 1u) % MC_NBUF;   // buffers of turn j and of turn j - 1
         const uint32_t tile = s_tid[cb];
         if (tile >= ntiles && prev >= ntiles) break;
-        PHASE_MARK(0);
         if (tile < ntiles && !mbar_wait(&bar[cb], (j / MC_NBUF) & 1u)) s_fail = 1u;
         __syncthreads();  // edges and the failure flag visible
-        PHASE_MARK(1);
         if (s_fail) {
             if (threadIdx.x == 0) atomicExch(&st->status, (uint32_t)DS_LOOKBACK_TIMEOUT);
             break;
@@ -1094,7 +1082,6 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
             const uint32_t flag = tile == 0u ? DESC_PREFIX : DESC_AGG;
             st_desc(desc + tile, ((unsigned long long)((tag << 2) | flag) << 32) | agg);
         }
-        PHASE_MARK(2);
 
         // ── pass 2: every warp compacts its touched spans in place (a span belongs to one warp) ──
 #pragma unroll 1
@@ -1134,7 +1121,6 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
             }
         }
         }
-        PHASE_MARK(3);
         uint32_t next_ticket = 0xFFFFFFFFu;
         if (prev < ntiles) {
         const uint32_t tile = prev;
@@ -1229,7 +1215,6 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                 st->epoch = e + 1u;
             }
         }
-        PHASE_MARK(4);
 
         // ── copy-out: every warp writes its four spans, each a contiguous run, with 16-byte stores:
         // a few single symbols bring the destination to a 16-byte boundary, then every store takes
@@ -1277,15 +1262,10 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
         // the buffer of turn j - 1 is free (or was never used): it takes the tile of turn j + MC_NBUF - 1
         if (threadIdx.x == 0) s_tid[pb] = next_ticket;
         __syncthreads();  // the buffer may be refilled; the new ticket is visible
-        PHASE_MARK(5);
-#ifdef B200BPE_PHASES
-        ph[6] += 1;
-#endif
         prev = tile;
         const uint32_t nt = s_tid[pb];
         if (nt < ntiles) fetch_tile(nt, pb); else more = false;
     }
-    PHASE_MARK(7);
     if (INCR && deltas) {
         // Fold this CTA's queue segment into the table.  Nobody else reads or writes the segment,
         // the updates commute with those of every other CTA, and doing it here, after the tiles,
@@ -1302,11 +1282,6 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
             t4[i] = make_uint4(0u, 0u, 0u, 0u);
         if (SHARD && blockIdx.x == 0 && threadIdx.x == 0) st->owned_inserted = 0u;
     }
-#ifdef B200BPE_PHASES
-    PHASE_MARK(7);
-    if (threadIdx.x == 0)
-        for (int k = 0; k < 8; k++) atomicAdd(&g_phase_cycles[k], (unsigned long long)ph[k]);
-#endif
 }
 
 // ─────────────────────────────── symbol buffer set-up ───────────────────────────────
