@@ -214,6 +214,11 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-profile", action="store_true", help="skip the extra run that times every kernel")
     ap.add_argument("--nccl-exchange", action="store_true", help="sharded runs: NCCL exchange instead of peer memory")
+    ap.add_argument("--corpus-mib", type=int, default=0, help="for profiler captures only: the first MiB of the configuration's corpus")
+    ap.add_argument("--encode-mib", type=int, default=0, help="for profiler captures only: encode this many MiB instead of config 4's 1024")
+    ap.add_argument("--budget-seconds", type=float, default=780.0,
+                    help="wall-clock budget of the whole command: the parts after the timed steps are shortened or left out "
+                         "(and named under \"skipped\") when they would not fit")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -235,8 +240,16 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     mode = args.mode or "fixed"
     kind, seed, nbytes, cfg_merges = CONFIGS[args.config]
+    full_corpus = not args.corpus_mib or args.corpus_mib * MIB >= nbytes
+    if not full_corpus:
+        nbytes = args.corpus_mib * MIB   # the generator is prefix-stable only per call: this is a different, smaller corpus
     n_goal = args.merges or cfg_merges
     L = _lib.lib()
+    t_begin = time.perf_counter()
+    skipped = []
+
+    def seconds_left() -> float:
+        return args.budget_seconds - (time.perf_counter() - t_begin)
 
     def barrier():
         if world > 1:
@@ -336,7 +349,7 @@ def main():
 
     # ── parity: the whole merge list and its counts against the golden list of the configuration ──
     parity = {"config": args.config, "mode": mode, "merges_compared": 0, "against": None}
-    gold = golden_merges(args.config, mode)
+    gold = golden_merges(args.config, mode) if full_corpus else None
     if gold is not None:
         k = min(n_merges, gold.shape[0])
         assert k == min(n_goal, gold.shape[0]), f"the run stopped after {n_merges} merges, the golden list has {gold.shape[0]}"
@@ -355,7 +368,22 @@ def main():
     # ── per-kernel device time: one more run with every kernel bracketed by CUDA events ──
     peak, peak_src = measured_hbm_peak()
     roofline = None
-    if not args.no_profile:
+    step_s = ms_per_step / 1e3
+    e2e_runs = args.e2e_runs
+    # what is still to come, in seconds: the end-to-end runs (the headline) are kept before everything else
+    need_e2e = lambda runs: (1 if runs > 0 else 0) * (1.15 * step_s + 2) + max(1, runs) * (1.15 * step_s + 2)
+    while e2e_runs > 0 and need_e2e(e2e_runs) > seconds_left() - 20:
+        e2e_runs -= 1
+    if e2e_runs != args.e2e_runs:
+        skipped.append(f"e2e runs cut from {args.e2e_runs} to {max(1, e2e_runs)}{'' if e2e_runs else ' (no untimed run before it)'}")
+    do_profile = not args.no_profile and (1.6 * step_s + 5) < seconds_left() - need_e2e(e2e_runs) - 20
+    if world > 1:   # every rank takes the same decisions
+        t = torch.tensor([e2e_runs, int(do_profile)], dtype=torch.int64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        e2e_runs, do_profile = int(t[0].item()), bool(t[1].item())
+    if not args.no_profile and not do_profile:
+        skipped.append("per-kernel timing run (roofline)")
+    if do_profile:
         prof = TrainerSession.create(engine, d_bytes.data_ptr(), d_mask.data_ptr(), n=my_n, device_pointers=True,
                                      target_vocab_size=256 + n_goal, compat_mode=mode, flags=flags | _lib.FLAG_TIME_KERNELS)
         barrier()
@@ -390,7 +418,8 @@ def main():
     out = np.zeros((n_goal, 3), np.uint32)
     cnt = np.zeros(n_goal, np.uint32)
     e2e_ms = []
-    for i in range(1 + max(1, args.e2e_runs)):
+    e2e_warm = 1 if e2e_runs > 0 else 0   # 0 runs asked for (or left by the budget): one timed run with no untimed one before it
+    for i in range(e2e_warm + max(1, e2e_runs)):
         flush.fill_(i & 0xFF)
         barrier()
         nm, es = C.c_uint32(), C.c_uint32()
@@ -402,7 +431,7 @@ def main():
         torch.cuda.synchronize()
         dt = max_over_ranks((time.perf_counter() - t0) * 1e3)
         barrier()
-        if i >= 1:
+        if i >= e2e_warm:
             e2e_ms.append(dt)
         assert np.array_equal(out[: nm.value], merges), "host-buffer run and resident run disagree"
     e2e_step = float(np.median(e2e_ms))
@@ -414,7 +443,10 @@ def main():
 
     # ── the CPU restatement on a bounded sample, and this library on exactly the same merges ──
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
+    do_cpu = not args.no_cpu and seconds_left() > 3 * args.cpu_seconds + 60
+    if not args.no_cpu and not do_cpu:
+        skipped.append("cpu_baseline sample")
+    if rank == 0 and world == 1 and do_cpu:
         cpu, r = cpu_sample(args.config, mode, args.cpu_seconds, args.ref_merges)
         k = cpu["merges"]
         if cpu["corpus_bytes"] == nbytes:
@@ -433,7 +465,16 @@ def main():
 
     # ── encode (config 4): documents sharded across ranks, no collective ──
     encode = None
-    if not args.no_encode:
+    do_encode = not args.no_encode and seconds_left() > 90
+    if world > 1:
+        t = torch.tensor([int(do_encode)], dtype=torch.int64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        do_encode = bool(t[0].item())
+    if not args.no_encode and not do_encode:
+        skipped.append("encode (config 4)")
+    enc_bytes = args.encode_mib * MIB if args.encode_mib else ENCODE_BYTES
+    enc_docs = max(1, ENCODE_DOCS * enc_bytes // ENCODE_BYTES)
+    if do_encode:
         gold3 = golden_merges(3, "fixed")
         if args.config == 3 and n_merges == 32000:
             vm = merges
@@ -447,11 +488,11 @@ def main():
         tok = TrieTokenizer.fromVocab(engine, vocab.entries)
         sub, lg = C.c_uint32(), C.c_uint32()
         L.b200bpe_tokenizer_layout(tok._h, C.byref(sub), C.byref(lg))
-        offs = synth.doc_offsets(ENCODE_SEED, ENCODE_BYTES, ENCODE_DOCS, 1.0)
+        offs = synth.doc_offsets(ENCODE_SEED, enc_bytes, enc_docs, 1.0)
         dcut = document_cuts(offs, world)
         d0, d1 = int(dcut[rank]), int(dcut[rank + 1])
         b0, b1 = int(offs[d0]), int(offs[d1])
-        my_text = synth.corpus_range(2, ENCODE_SEED, ENCODE_BYTES, b0, b1 - b0)
+        my_text = synth.corpus_range(2, ENCODE_SEED, enc_bytes, b0, b1 - b0)
         my_offs = (offs[d0:d1 + 1] - offs[d0]).astype(np.uint64)
         d_text = torch.from_numpy(my_text).cuda()
         d_offs = torch.from_numpy(my_offs.view(np.int64).copy()).cuda()
@@ -499,14 +540,14 @@ def main():
         tot_tok = sum_over_ranks(ntok)
         w_ms, c_ms = float(np.mean(walk_ms)), float(np.mean(comp_ms))
         alg_bytes = (b1 - b0) + 4 * ntok
-        encode = {"metric": "encode_GB_per_s", "value": ENCODE_BYTES / 1e9 / (float(np.mean(enc_ms)) / 1e3), "unit": "GB/s",
-                  "workload": f"config4: {ENCODE_BYTES // MIB} MiB synthetic UTF-8 (seed {ENCODE_SEED}) in {ENCODE_DOCS} lognormal documents, "
+        encode = {"metric": "encode_GB_per_s", "value": enc_bytes / 1e9 / (float(np.mean(enc_ms)) / 1e3), "unit": "GB/s",
+                  "workload": f"config4: {enc_bytes // MIB} MiB synthetic UTF-8 (seed {ENCODE_SEED}) in {enc_docs} lognormal documents, "
                               f"{len(vocab.entries)}-entry vocabulary (the merge list of config 3), chunk {tok.chunkSize}",
                   "trie": {"nodes": tok.nodeCount, "edges": tok.edgeCount, "max_token_len": tok.maxTokenLen,
                            "layout": {0: "global hash table behind a probe cache", 1: "hybrid: hot transitions in shared memory, two-byte first step"}.get(sub.value, "shared-memory cuckoo table"),
                            "log2_slots": lg.value},
                   "tokens": tot_tok, "walk_ms": w_ms, "scan_compact_ms": c_ms, "scaling": "strong",
-                  "e2e_GB_per_s": ENCODE_BYTES / 1e9 / (float(np.mean(e_ms)) / 1e3),
+                  "e2e_GB_per_s": enc_bytes / 1e9 / (float(np.mean(e_ms)) / 1e3),
                   "e2e_h2d_bytes": int(b1 - b0 + 8 * (d1 - d0 + 1)), "e2e_d2h_bytes": int(4 * ntok + 8 * (d1 - d0 + 1)),
                   "parity": enc_parity,
                   "roofline": {"bound": "hbm", "kernel": "k_trie_walk", "achieved": alg_bytes / 1e9 / (w_ms / 1e3),
@@ -525,7 +566,7 @@ def main():
             "parallelism": "single GPU" if world == 1 else f"corpus cut at word starts over {world} GPUs, {exchange} count exchange",
             "l2": f"inputs ({4 * nbytes // world // MIB} MiB of symbols per buffer and rank) exceed L2; a 256 MiB buffer is rewritten between steps",
             "setup_s": setup_s, "e2e": e2e, "gpu_launches": int(gpu_launches), "clocks": clocks, "roofline": roofline,
-            "cpu_baseline": cpu, "encode": encode, "pretokenize": pretok, "parity": parity,
+            "cpu_baseline": cpu, "encode": encode, "pretokenize": pretok, "parity": parity, "skipped": skipped,
         }))
     if world > 1:
         dist.destroy_process_group()

@@ -103,6 +103,20 @@ struct PeerExchange {
     }
 };
 
+// Collective over the job's ranks: every rank leaves with the largest v of any rank.
+static b200bpe_status agree_on_max(Ctx* ctx, unsigned long long* v) {
+    if (ctx->world <= 1) return B200BPE_OK;
+    unsigned long long* d = nullptr;
+    B2_CUDA(cudaMalloc(&d, 8));
+    B2_CUDA(cudaMemcpyAsync(d, v, 8, cudaMemcpyHostToDevice, ctx->stream));
+    const int rc = ctx->nccl.AllReduce(d, d, 1, /*ncclUint64*/ 5, /*ncclMax*/ 2, ctx->comm, ctx->stream);
+    if (rc) { cudaFree(d); set_last_error("ncclAllReduce failed"); return B200BPE_ERR_NCCL; }
+    B2_CUDA(cudaMemcpyAsync(v, d, 8, cudaMemcpyDeviceToHost, ctx->stream));
+    B2_CUDA(cudaStreamSynchronize(ctx->stream));
+    cudaFree(d);
+    return B200BPE_OK;
+}
+
 struct Trainer {
     Ctx* ctx = nullptr;
     uint64_t n0 = 0;            // symbols at creation (this rank)
@@ -188,6 +202,14 @@ b200bpe_status Trainer::alloc_common() {
     // shrink in proportion to the shard; too small a start costs a chain of grow-and-recount restarts)
     if (table_log2 == 0) table_log2 = std::min<uint32_t>(21, std::max<uint32_t>(15, ceil_log2(n0 * (uint64_t)ctx->world / 128 + 1)));
     table_log2 = std::min(table_log2, MAX_TABLE_LOG2);
+    if (ctx->world > 1) {
+        // The ranks' spans differ by a few bytes, which can put them either side of a power of two; the exchange
+        // buffers are laid out from the table size, so every rank takes the largest any rank chose.
+        unsigned long long v = table_log2;
+        b200bpe_status r = agree_on_max(ctx, &v);
+        if (r) return r;
+        table_log2 = (uint32_t)v;
+    }
     B2_CUDA(cudaMalloc(&table, sizeof(PairSlot) << table_log2));
     B2_CUDA(cudaMalloc(&d_state, sizeof(DevState)));
     B2_CUDA(cudaMallocHost(&h_state, sizeof(DevState)));
