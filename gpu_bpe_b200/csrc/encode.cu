@@ -714,6 +714,8 @@ b200bpe_status b200bpe_tokenizer_create(b200bpe_ctx* c, const void* trie, size_t
     return b200bpe_tokenizer_create_ex(c, trie, len, &o, out);
 }
 
+static b200bpe_status noalloc_scratch_for(int device, unsigned char** out);
+
 b200bpe_status b200bpe_tokenizer_create_ex(b200bpe_ctx* c, const void* trie, size_t len, const b200bpe_tok_opts* opts,
                                            b200bpe_tok** out) {
     if (!c || !trie || !out || !opts || opts->struct_size != sizeof(b200bpe_tok_opts)) return B200BPE_ERR_BAD_ARG;
@@ -1067,6 +1069,16 @@ b200bpe_status b200bpe_tokenizer_create_ex(b200bpe_ctx* c, const void* trie, siz
     B2_TRY(cudaMalloc(&t->d_total, 8));
     B2_TRY(cudaMallocHost(&t->h_total, 16));
     for (auto& e : t->ev) B2_TRY(cudaEventCreate(&e));
+    {
+        // Whatever the driver sets up lazily for the encode kernels and for the scratch array of
+        // b200bpe_encode_device_noalloc is set up here, so that that entry point finds it all in place:
+        // the compaction kernel is loaded (the walk kernels were, by the attribute calls above) and
+        // the array's device address is looked up.
+        cudaFuncAttributes fa;
+        B2_TRY(cudaFuncGetAttributes(&fa, k_scan_compact));
+        unsigned char* scratch = nullptr;
+        if (noalloc_scratch_for(c->c.device, &scratch) != B200BPE_OK) return fail(B200BPE_ERR_CUDA);
+    }
     t->trans_bytes = trans.size() * 8;
     B2_TRY(cudaStreamSynchronize(s));
 #undef B2_TRY
@@ -1244,7 +1256,9 @@ constexpr uint64_t NOALLOC_MAX_BYTES = 1ull << 20;   // largest input of one cal
 constexpr uint64_t NOALLOC_MAX_CHUNKS = 8192;        // largest number of chunks of one call
 constexpr uint64_t NA_ALIGN = 256;
 constexpr uint64_t na_up(uint64_t x) { return (x + NA_ALIGN - 1) / NA_ALIGN * NA_ALIGN; }
-// staging holds chunk_size tokens per chunk: at most the input length rounded up to one more chunk
+// Staging holds a row of chunk_size words per chunk.  A walk writes at most one word per input byte
+// (the cuckoo and hash walks in whole 8-word sectors), so a call uses at most n + 8 words of it; the
+// array reserves twice the largest input, and the second half is never touched.
 constexpr uint64_t NA_OFF_STAGING = 0;
 constexpr uint64_t NA_STAGING_BYTES = na_up((NOALLOC_MAX_BYTES + NOALLOC_MAX_BYTES) * 4);
 constexpr uint64_t NA_OFF_COUNTS = NA_OFF_STAGING + NA_STAGING_BYTES;

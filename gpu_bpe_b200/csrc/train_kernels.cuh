@@ -862,20 +862,23 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
     const uint32_t AB = A | (B << 16);  // the low halves of a pair that may merge
 
 
-    // Start the copy of a tile into buffer b: thread 0 issues the bulk copy, threads 32..35 fetch the
-    // edges.  Callers make sure (barrier) that nobody still reads the buffer.
+    // Start the copy of a tile into buffer b.  One bulk copy brings the tile together with the four words
+    // before it (the last of them is the left edge) and the four after it (the right edge; the arrays are
+    // allocated with that much room behind the last symbol, and what lies at or beyond N there is never
+    // used: a span that can see it is not `interior` and masks by position).  Callers make sure (barrier)
+    // that nobody still reads the buffer.
     auto fetch_tile = [&](uint32_t tile, uint32_t b) {
         uint32_t* const in = mc_smem + b * BUF_WORDS + 4;
         const uint32_t i0 = tile * MC_TILE;
         if (threadIdx.x == 0) {
-            const uint32_t bytes = ((min((uint32_t)MC_TILE, N - i0) + 3u) & ~3u) * 4u;
+            const uint32_t bytes = ((min((uint32_t)MC_TILE, N - i0) + 3u) & ~3u) * 4u + 16u;
             fence_proxy_async_smem();
-            bulk_load(in, src + i0, bytes, &bar[b]);
-        } else if (threadIdx.x == 32) {
-            in[-1] = i0 > 0u ? src[i0 - 1u] : 0u;
-        } else if (threadIdx.x >= 33 && threadIdx.x < 36) {
-            const uint32_t k = threadIdx.x - 33u, i = i0 + MC_TILE + k;
-            in[MC_TILE + k] = i < N ? src[i] : 0u;
+            if (i0 > 0u) {
+                bulk_load(in - 4, src + i0 - 4u, bytes + 16u, &bar[b]);
+            } else {
+                in[-1] = 0u;
+                bulk_load(in, src, bytes, &bar[b]);
+            }
         }
     };
 

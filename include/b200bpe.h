@@ -231,9 +231,11 @@ b200bpe_status b200bpe_encode_batch_device(b200bpe_tok*, const uint8_t* d_bytes,
  * cudaFree or other allocating call: for encode steps inside a latency-critical or
  * memory-exhausted process, where the allocator's locks, its implicit synchronisation or its
  * failure are not acceptable.  Limits: n <= 1 MiB and at most 8,192 chunks per call; larger
- * inputs return B200BPE_ERR_CAPACITY (b200bpe_last_error() says why).  The first call on a device
- * looks up the array's device address, so make it before any stream capture begins.  All calls on
- * a device share the array: calls that overlap on the GPU race; one at a time per device. */
+ * inputs return B200BPE_ERR_CAPACITY (b200bpe_last_error() says why).  The array's device address
+ * is looked up and the kernels are loaded when the tokenizer is created, not here.  With the
+ * global-table trie layout this entry point does not set the persisting L2 window that the pooled
+ * path asks for.  All calls on a device share the array: calls that overlap on the GPU race; one
+ * at a time per device. */
 b200bpe_status b200bpe_encode_device_noalloc(b200bpe_tok*, const uint8_t* d_bytes, uint64_t n, uint32_t* d_tokens_out,
                                              uint64_t cap, uint64_t* n_tokens_out);
 /* Milliseconds of device time of the last encode call, split by kernel: walk, scan+compaction. */
