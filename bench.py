@@ -48,7 +48,7 @@ MARGIN = 1 * MIB   # bytes a rank generates either side of its nominal span to f
 # DRAM bytes (read + write) per algorithmic byte, from one ncu capture of each kernel (the summaries
 # under profiles/ give the commands): the roofline "traffic" is this ratio times the algorithmic
 # bytes of an average launch of the run.
-NCU_DRAM_PER_ALGORITHMIC_BYTE = {"pair_count": 1.02, "argmax": 1.00, "merge_compact": 0.93, "trie_walk": 1.05}
+NCU_DRAM_PER_ALGORITHMIC_BYTE = {"pair_count": 1.02, "argmax": 1.00, "merge_compact": 0.93, "trie_walk": 2.03}
 
 
 def workload_name(cfg: int, nbytes: int, merges: int, seed: int) -> str:
