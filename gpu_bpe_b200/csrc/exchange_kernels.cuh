@@ -39,10 +39,12 @@ k_partition(DevState* __restrict__ st, PairSlot* __restrict__ table, PairSlot* _
     // Room in a bucket is reserved once per warp and owner (match-any), not once per entry: the
     // `world` fill counters would otherwise take one atomic for every live pair of the table.
     const int lane = threadIdx.x & 31;
+    uint32_t used = 0u;   // slots that hold a key, dead or alive: the table's fill, for the decision to grow
     for (uint32_t i0 = blockIdx.x * blockDim.x + (threadIdx.x & ~31u); i0 < C; i0 += gridDim.x * blockDim.x) {
         const uint32_t i = i0 + lane;
         const uint4 q = i < C ? __ldcg(t4 + i) : make_uint4(0u, 0u, 0u, 0u);
         const unsigned long long key = ((unsigned long long)q.y << 32) | q.x;
+        used += key != 0ull ? 1u : 0u;
         const bool live = key != 0ull && !(keep && q.z == 0u);
         const uint32_t o = live ? owner_of(hash_pair(key), world) : 0xFFFFFFFFu;
         const uint32_t peers = __match_any_sync(0xFFFFFFFFu, o);
@@ -60,6 +62,11 @@ k_partition(DevState* __restrict__ st, PairSlot* __restrict__ table, PairSlot* _
             if (!keep) __stcg(t4 + i, make_uint4(0u, 0u, 0u, 0u));
         }
     }
+    if (keep) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) used += __shfl_xor_sync(0xFFFFFFFFu, used, o);
+        if (lane == 0 && used) atomicAdd(&st->occupied, used);
+    }
 }
 
 // Write the bucket headers and reset the fill counters for the next merge.
@@ -67,6 +74,12 @@ __global__ void k_seal_buckets(DevState* __restrict__ st, PairSlot* __restrict__
                                uint32_t cap, uint32_t world) {
     const uint32_t o = threadIdx.x;
     if (o >= world) return;
+    if (o == 0u) {
+        // a local table that is kept from merge to merge and is more than half full grows at the end of the batch
+        // (without this it would only grow after a chain of 1,024 failed probes)
+        if (st->incremental != 0u && (unsigned long long)st->occupied * 2ull > (1ull << st->table_log2)) st->want_grow = 1u;
+        st->occupied = 0u;
+    }
     const bool idle = (st->early_stop | st->target_hit) != 0u;
     const uint32_t f = idle ? 0u : min(fill[o], cap - 1u);
     buckets[(size_t)o * cap].key = 0ull;

@@ -589,7 +589,7 @@ k_argmax_setup(DevState* __restrict__ st, PairSlot* table, CtaBest* __restrict__
             occ += socc[w];
         }
         st->argmax_done = 0u;
-        st->occupied = occ;
+        st->occupied = mode == 1 ? 0u : occ;   // sharded: the word is the partition kernel's running count of the local table's fill
         if ((unsigned long long)occ * 2ull > (unsigned long long)C) st->want_grow = 1u;
         if (mode == 0) {
             if (listed) {
