@@ -25,7 +25,10 @@ constexpr int PC_IDLE_CTAS = 64;     // pair count: CTAs that stay when there is
 constexpr int PC_LOCAL_PROBES = 2;   // linear probes in shared memory before going to the global table
 constexpr int TABLE_MAX_PROBE = 1024;
 constexpr int AM_THREADS = 256;
-constexpr int MC_THREADS = 256;
+#ifndef B200BPE_MC_THREADS
+#define B200BPE_MC_THREADS 256
+#endif
+constexpr int MC_THREADS = B200BPE_MC_THREADS;   // merge kernel: threads per CTA
 #ifndef B200BPE_MC_ROWS
 #define B200BPE_MC_ROWS 4
 #endif
