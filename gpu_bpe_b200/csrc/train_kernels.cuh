@@ -957,6 +957,12 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
             uint4 q[MC_ROWS];
 #pragma unroll
             for (int j = 0; j < MC_ROWS; j++) q[j] = reinterpret_cast<const uint4*>(in + lw)[j * 32 + lane];
+            // the symbol before the span and the three after it: one load by lanes 0..3 next to the rows' loads, handed
+            // round by shuffles (a load inside a one-lane branch would put a shared-memory round trip into the chain)
+            uint32_t edge_sym = 0u;
+            if (lane < 4) edge_sym = snapshot(lane == 0 ? in[(int)lw - 1] : in[lw + MC_ROWS * 128u + (lane - 1)]);
+            const uint32_t s_prev = __shfl_sync(0xFFFFFFFFu, edge_sym, 0), s_n0 = __shfl_sync(0xFFFFFFFFu, edge_sym, 1);
+            const uint32_t s_n1 = __shfl_sync(0xFFFFFFFFu, edge_sym, 2), s_n2 = __shfl_sync(0xFFFFFFFFu, edge_sym, 3);
             // Candidate test first: two neighbouring symbols can only merge if their low halves are
             // (a, b), one byte permute and one compare per pair.  Every lane tests the four pairs that
             // begin at its own symbols; lane 0 adds the pair that begins at the symbol before the span,
@@ -967,15 +973,13 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
             for (int j = 0; j < MC_ROWS; j++) {
                 uint32_t nx = __shfl_down_sync(0xFFFFFFFFu, q[j].x, 1);
                 const uint32_t rx = __shfl_sync(0xFFFFFFFFu, q[j < MC_ROWS - 1 ? j + 1 : j].x, 0);
-                if (lane == 31) nx = j < MC_ROWS - 1 ? rx : snapshot(in[lw + MC_ROWS * 128u]);
+                if (lane == 31) nx = j < MC_ROWS - 1 ? rx : s_n0;
                 cand |= __byte_perm(q[j].x, q[j].y, 0x5410) == AB || __byte_perm(q[j].y, q[j].z, 0x5410) == AB ||
                         __byte_perm(q[j].z, q[j].w, 0x5410) == AB || __byte_perm(q[j].w, nx, 0x5410) == AB;
             }
-            if (lane == 0) cand |= __byte_perm(snapshot(in[(int)lw - 1]), q[0].x, 0x5410) == AB;
+            if (lane == 0) cand |= __byte_perm(s_prev, q[0].x, 0x5410) == AB;
             if (INCR && lane == 31) {
-                const uint32_t n0 = snapshot(in[lw + MC_ROWS * 128u]), n1 = snapshot(in[lw + MC_ROWS * 128u + 1u]);
-                const uint32_t n2 = snapshot(in[lw + MC_ROWS * 128u + 2u]);
-                cand |= __byte_perm(n0, n1, 0x5410) == AB || __byte_perm(n1, n2, 0x5410) == AB;
+                cand |= __byte_perm(s_n0, s_n1, 0x5410) == AB || __byte_perm(s_n1, s_n2, 0x5410) == AB;
             }
             uint32_t kb = MC_KEEP_ALL, rew = 0u;   // per row one byte: own symbol kept (low nibble), rewritten (high nibble)
             if (!interior || __any_sync(0xFFFFFFFFu, cand)) {
@@ -994,7 +998,7 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
             // the symbol before the span (lane 0) and the three after it (lanes 1..3): bit 0 = is `a`, bit 1 = is a mergeable `b`
             uint32_t edge = 0u;
             if (lane < 4) {
-                const uint32_t v = snapshot(lane == 0 ? in[(int)lw - 1] : in[lw + MC_ROWS * 128u + (lane - 1)]);
+                const uint32_t v = edge_sym;
                 edge = ((v & TOKEN_MASK) == A ? 1u : 0u) | ((v & (TOKEN_MASK | WORD_START_BIT)) == B ? 2u : 0u);
             }
             const uint32_t e_prev = __shfl_sync(0xFFFFFFFFu, edge, 0), e_n0 = __shfl_sync(0xFFFFFFFFu, edge, 1);
