@@ -217,7 +217,7 @@ def main():
     ap.add_argument("--ref-seconds", type=float, default=10.0, help="CPU arm: time bound of one step")
     ap.add_argument("--ref-merges", type=int, default=64, help="CPU arm: most merges of one step")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
-    ap.add_argument("--e2e-runs", type=int, default=2)
+    ap.add_argument("--e2e-runs", type=int, default=3)
     ap.add_argument("--no-encode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-profile", action="store_true", help="skip the extra run that times every kernel")
