@@ -1256,18 +1256,18 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
             const uint4* sp4 = reinterpret_cast<const uint4*>(sp);
             uint4* __restrict__ d4 = reinterpret_cast<uint4*>(dst + off + head);
             if ((uint32_t)lane < head) dst[off + lane] = sp[lane];
-            if (cnt == MC_ROWS * 128u) {
-                // A span that kept everything, which is nearly every span of a sparse merge: the same stores with
-                // a trip count known at compile time, so that all loads of the span are in flight together.
+            {
+                // The trip count is known at compile time (a span has at most 128 * MC_ROWS / 4 vectors per lane row),
+                // so all shared-memory loads of the span are in flight together; vectors beyond the span's kept count
+                // are loaded (the buffer holds four more words behind every span) but not stored.
                 uint4 lo[MC_ROWS], hi[MC_ROWS];
 #pragma unroll
                 for (int it = 0; it < MC_ROWS; it++) lo[it] = sp4[it * 32 + lane];
                 if (head == 0u) {
 #pragma unroll
-                    for (int it = 0; it < MC_ROWS; it++) d4[it * 32 + lane] = lo[it];
+                    for (int it = 0; it < MC_ROWS; it++)
+                        if ((uint32_t)(it * 32 + lane) < nvec) d4[it * 32 + lane] = lo[it];
                 } else {
-                    // (the last lane's second load of the last row reads the first words after the span, which the
-                    // buffer holds; its vector is not stored: nvec is 128 * MC_ROWS - 1 here)
 #pragma unroll
                     for (int it = 0; it < MC_ROWS; it++) hi[it] = sp4[it * 32 + lane + 1];
                     if (head == 1u) {
@@ -1283,23 +1283,6 @@ k_merge_compact(DevState* __restrict__ st, uint32_t* buf0, uint32_t* buf1, unsig
                         for (int it = 0; it < MC_ROWS; it++)
                             if ((uint32_t)(it * 32 + lane) < nvec) d4[it * 32 + lane] = make_uint4(lo[it].w, hi[it].x, hi[it].y, hi[it].z);
                     }
-                }
-            } else if (head == 0u) {
-                for (uint32_t i = lane; i < nvec; i += 32) d4[i] = sp4[i];
-            } else if (head == 1u) {
-                for (uint32_t i = lane; i < nvec; i += 32) {
-                    const uint4 lo = sp4[i], hi = sp4[i + 1];
-                    d4[i] = make_uint4(lo.y, lo.z, lo.w, hi.x);
-                }
-            } else if (head == 2u) {
-                for (uint32_t i = lane; i < nvec; i += 32) {
-                    const uint4 lo = sp4[i], hi = sp4[i + 1];
-                    d4[i] = make_uint4(lo.z, lo.w, hi.x, hi.y);
-                }
-            } else {
-                for (uint32_t i = lane; i < nvec; i += 32) {
-                    const uint4 lo = sp4[i], hi = sp4[i + 1];
-                    d4[i] = make_uint4(lo.w, hi.x, hi.y, hi.z);
                 }
             }
             const uint32_t done = head + 4u * nvec;
